@@ -1,0 +1,238 @@
+"""ctypes binding of libflexattn.so (the C ABI declared in include/flexattn.h).
+
+This is the only backend: there is no CPU or PyTorch fallback.  Importing the module without the built
+library raises, and every call checks the returned status.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from collections import OrderedDict
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libflexattn.so")
+
+DTYPE_BF16, DTYPE_F32 = 0, 1
+SCORE_NONE, SCORE_ALIBI, SCORE_SOFTCAP = 0, 1, 2
+MASK_NONE, MASK_CAUSAL, MASK_SLIDING_WINDOW, MASK_SLIDING_WINDOW_CAUSAL, MASK_DOCUMENT, MASK_S2 = range(6)
+BACKEND_AUTO, BACKEND_SIMT, BACKEND_TCGEN05 = 0, 1, 2
+TILE = 128
+
+MASK_KIND_IDS = {"none": MASK_NONE, "causal": MASK_CAUSAL, "sliding_window": MASK_SLIDING_WINDOW,
+                 "sliding_window_causal": MASK_SLIDING_WINDOW_CAUSAL, "document": MASK_DOCUMENT, "s2": MASK_S2}
+SCORE_KIND_IDS = {"none": SCORE_NONE, "alibi": SCORE_ALIBI, "softcap": SCORE_SOFTCAP}
+BACKEND_IDS = {"auto": BACKEND_AUTO, "simt": BACKEND_SIMT, "tcgen05": BACKEND_TCGEN05}
+
+
+class FlexAttnParams(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("o", ctypes.c_void_p),
+        ("d_o", ctypes.c_void_p), ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
+        ("l", ctypes.c_void_p), ("m", ctypes.c_void_p), ("delta", ctypes.c_void_p),
+        ("doc_ids", ctypes.c_void_p), ("alibi_slopes", ctypes.c_void_p),
+        ("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seq_q", ctypes.c_int32),
+        ("seq_k", ctypes.c_int32), ("head_dim", ctypes.c_int32),
+        ("dtype", ctypes.c_int32), ("sm_scale", ctypes.c_float),
+        ("score_kind", ctypes.c_int32), ("softcap", ctypes.c_float),
+        ("mask_kind", ctypes.c_int32), ("window", ctypes.c_int32), ("stride", ctypes.c_int32),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+        ("status", ctypes.c_void_p), ("backend", ctypes.c_int32), ("reserved", ctypes.c_int32),
+    ]
+
+
+class FlexAttnError(RuntimeError):
+    def __init__(self, code, where):
+        self.code = code
+        super().__init__(f"{where}: {status_string(code)} (status {code})")
+
+
+def _load():
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            f"{_LIB_PATH} is missing: build it with `python -m flex_attention_tpu_b200.build` "
+            "(there is no fallback implementation)")
+    lib = ctypes.CDLL(_LIB_PATH)
+    P = ctypes.POINTER(FlexAttnParams)
+    lib.flexattn_abi_version.restype = ctypes.c_int
+    lib.flexattn_status_string.restype = ctypes.c_char_p
+    lib.flexattn_status_string.argtypes = [ctypes.c_int]
+    lib.flexattn_workspace_bytes.restype = ctypes.c_size_t
+    lib.flexattn_workspace_bytes.argtypes = [P]
+    for name in ("flexattn_build_mask_map", "flexattn_fwd", "flexattn_bwd_preprocess", "flexattn_bwd_dq",
+                 "flexattn_bwd_dkv"):
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_void_p, P]
+    lib.flexattn_read_mask_map.restype = ctypes.c_int
+    lib.flexattn_read_mask_map.argtypes = [ctypes.c_void_p, P, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                           ctypes.POINTER(ctypes.c_int32)]
+    lib.flexattn_selftest_umma.restype = ctypes.c_int
+    lib.flexattn_selftest_umma.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                           ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p,
+                                           ctypes.POINTER(ctypes.c_int32)]
+    if lib.flexattn_abi_version() != 1:
+        raise ImportError("libflexattn.so ABI version mismatch: rebuild the library")
+    return lib
+
+
+lib = _load()
+
+
+def status_string(code: int) -> str:
+    return lib.flexattn_status_string(int(code)).decode()
+
+
+def check(code: int, where: str):
+    if code != 0:
+        raise FlexAttnError(code, where)
+
+
+def _stream_ptr(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+class Problem:
+    """One attention problem: shapes, score/mask spec and the tensors bound so far.  Owns the mask-map
+    workspace (a torch buffer) and rebuilds the map only when the mask inputs change."""
+
+    _map_cache: "OrderedDict[tuple, torch.Tensor]" = OrderedDict()
+    _MAP_CACHE_ENTRIES = 16
+
+    def __init__(self, q, k, *, sm_scale, mask_kind=MASK_NONE, window=0, stride=0, doc_ids=None,
+                 score_kind=SCORE_NONE, softcap=0.0, alibi_slopes=None, backend=BACKEND_AUTO, status=None):
+        if not q.is_cuda:
+            raise ValueError("flex attention tensors must live on a CUDA device (no CPU path exists)")
+        if q.dim() != 4 or k.dim() != 4:
+            raise ValueError("expected [batch, heads, seq, head_dim] tensors")
+        if q.dtype not in (torch.bfloat16, torch.float32):
+            raise NotImplementedError(f"dtype {q.dtype} is not supported (bfloat16 or float32)")
+        self.device = q.device
+        self.dtype = q.dtype
+        B, H, Sq, D = q.shape
+        self.shape_q = (B, H, Sq, D)
+        self.shape_k = tuple(k.shape)
+        p = FlexAttnParams()
+        p.batch, p.heads, p.seq_q, p.seq_k, p.head_dim = B, H, Sq, k.shape[2], D
+        p.dtype = DTYPE_BF16 if q.dtype == torch.bfloat16 else DTYPE_F32
+        p.sm_scale = float(sm_scale)
+        p.score_kind, p.softcap = int(score_kind), float(softcap)
+        p.mask_kind, p.window, p.stride = int(mask_kind), int(window), int(stride)
+        p.backend = int(backend)
+        self._keep = []  # tensors whose pointers sit in `p`
+        if mask_kind == MASK_DOCUMENT:
+            if doc_ids is None:
+                raise ValueError("document mask needs segment/doc ids")
+            doc_ids = torch.as_tensor(doc_ids)
+            if doc_ids.dim() == 1:
+                doc_ids = doc_ids[None].expand(B, -1)
+            doc_ids = doc_ids.to(device=self.device, dtype=torch.int32).contiguous()
+            if doc_ids.shape != (B, max(Sq, k.shape[2])):
+                raise ValueError(f"doc ids must be [batch, {max(Sq, k.shape[2])}], got {tuple(doc_ids.shape)}")
+            p.doc_ids = doc_ids.data_ptr()
+            self._keep.append(doc_ids)
+        self.doc_ids = doc_ids if mask_kind == MASK_DOCUMENT else None
+        if score_kind == SCORE_ALIBI:
+            slopes = torch.as_tensor(alibi_slopes, dtype=torch.float32).flatten()
+            if slopes.numel() == 1:
+                slopes = slopes.expand(H)
+            if slopes.numel() != H:
+                raise ValueError(f"need one ALiBi slope per head ({H}), got {slopes.numel()}")
+            slopes = slopes.to(self.device).contiguous()
+            p.alibi_slopes = slopes.data_ptr()
+            self._keep.append(slopes)
+        if status is not None:
+            p.status = status.data_ptr()
+            self._keep.append(status)
+        self.p = p
+        self._bind_workspace()
+
+    # ------------------------------------------------------------------ mask map
+    def _bind_workspace(self):
+        p = self.p
+        nbytes = lib.flexattn_workspace_bytes(ctypes.byref(p))
+        if nbytes == 0:
+            raise FlexAttnError(2, "flexattn_workspace_bytes")
+        doc_key = None
+        if self.doc_ids is not None:
+            doc_key = (self.doc_ids.data_ptr(), self.doc_ids._version)
+        key = (self.device.index, p.mask_kind, p.window, p.stride, p.batch, p.seq_q, p.seq_k, doc_key)
+        cache = Problem._map_cache
+        ws = cache.get(key) if doc_key is None else None  # doc id buffers can be recycled: always rebuild
+        fresh = ws is None
+        if fresh:
+            ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        p.workspace, p.workspace_bytes = ws.data_ptr(), nbytes
+        self.workspace = ws
+        if fresh:
+            check(lib.flexattn_build_mask_map(_stream_ptr(self.device), ctypes.byref(p)), "flexattn_build_mask_map")
+            if doc_key is None:
+                cache[key] = ws
+                while len(cache) > Problem._MAP_CACHE_ENTRIES:
+                    cache.popitem(last=False)
+
+    def read_map(self, which: int, b: int, index: int):
+        out = (ctypes.c_int32 * 4)()
+        check(lib.flexattn_read_mask_map(_stream_ptr(self.device), ctypes.byref(self.p), which, b, index, out),
+              "flexattn_read_mask_map")
+        return tuple(out)
+
+    # ------------------------------------------------------------------ tensors
+    def _bind(self, **tensors):
+        for name, t in tensors.items():
+            if t is None:
+                continue
+            if not t.is_cuda or t.device != self.device:
+                raise ValueError(f"{name} must be on {self.device}")
+            if not t.is_contiguous():
+                raise ValueError(f"{name} must be contiguous")
+            want = torch.float32 if name in ("l", "m", "delta") else self.dtype
+            if t.dtype != want:
+                raise ValueError(f"{name} must be {want}, got {t.dtype}")
+            setattr(self.p, name, t.data_ptr())
+            self._keep.append(t)
+
+    def _new(self, shape, dtype=None):
+        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+    def forward(self, q, k, v):
+        B, H, Sq, D = self.shape_q
+        o, l, m = self._new(self.shape_q), self._new((B, H, Sq), torch.float32), self._new((B, H, Sq), torch.float32)
+        self._bind(q=q, k=k, v=v, o=o, l=l, m=m)
+        check(lib.flexattn_fwd(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_fwd")
+        return o, l, m
+
+    def preprocess(self, o, do):
+        B, H, Sq, _ = self.shape_q
+        delta = self._new((B, H, Sq), torch.float32)
+        self._bind(o=o, d_o=do, delta=delta)
+        check(lib.flexattn_bwd_preprocess(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_preprocess")
+        return delta
+
+    def bwd_dq(self, q, k, v, do, l, m, delta):
+        dq = self._new(self.shape_q)
+        self._bind(q=q, k=k, v=v, d_o=do, l=l, m=m, delta=delta, dq=dq)
+        check(lib.flexattn_bwd_dq(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_dq")
+        return dq
+
+    def bwd_dkv(self, q, k, v, do, l, m, delta):
+        dk, dv = self._new(self.shape_k), self._new(self.shape_k)
+        self._bind(q=q, k=k, v=v, d_o=do, l=l, m=m, delta=delta, dk=dk, dv=dv)
+        check(lib.flexattn_bwd_dkv(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_dkv")
+        return dk, dv
+
+
+def selftest_umma(variant: int, a: torch.Tensor, b: torch.Tensor, tuning=None, status=None) -> torch.Tensor:
+    """Single-tile tensor-core self check (see flexattn_selftest_umma in the header)."""
+    kdim = a.shape[1]
+    d = torch.empty(128, 128, dtype=torch.float32, device=a.device)
+    tune = None
+    if tuning is not None:
+        tune = (ctypes.c_int32 * 4)(*(list(tuning) + [0] * 4)[:4])
+    check(lib.flexattn_selftest_umma(_stream_ptr(a.device), int(variant), _ptr(a), _ptr(b), _ptr(d), int(kdim),
+                                     _ptr(status), tune), "flexattn_selftest_umma")
+    return d

@@ -1,0 +1,140 @@
+// Internal definitions shared by every translation unit of libflexattn.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../../include/flexattn.h"
+
+namespace flexattn {
+
+constexpr int kTile = FLEXATTN_TILE;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+// Finite stand-in for -inf (log2 domain in the tensor-core kernels, natural units in the SIMT ones):
+// a row whose keys so far are all masked keeps m == kMasked, its garbage weights exp(0) == 1 are
+// wiped by alpha == exp(kMasked - m_new) == 0 as soon as a kept key arrives.  The reference kernels use
+// -0.7 * FLT_MAX for the same reason (flex_attention_kernel.py:288).
+constexpr float kMasked = -1.0e30f;
+
+// ---------------------------------------------------------------------------------------------
+// Mask map (lives in the caller's workspace).
+// ---------------------------------------------------------------------------------------------
+struct MapHeader {
+  int32_t magic, mask_kind, window, stride;
+  int32_t seq_q, seq_k, n_qt, n_kt;
+  int32_t rows;  // batch for document masks, else 1
+  int32_t pad[7];
+};
+constexpr int32_t kMapMagic = 0x464c5841;  // "FLXA"
+
+struct MapLayout {
+  int n_qt, n_kt, rows, n_t;
+  size_t off_row, off_col, off_doc, bytes;
+};
+
+__host__ __device__ inline MapLayout map_layout(int batch, int seq_q, int seq_k, int mask_kind) {
+  MapLayout L;
+  L.n_qt = (seq_q + kTile - 1) / kTile;
+  L.n_kt = (seq_k + kTile - 1) / kTile;
+  L.n_t = L.n_qt > L.n_kt ? L.n_qt : L.n_kt;
+  L.rows = (mask_kind == FLEXATTN_MASK_DOCUMENT) ? batch : 1;
+  L.off_row = sizeof(MapHeader);
+  L.off_col = L.off_row + sizeof(int4) * (size_t)L.rows * L.n_qt;
+  L.off_doc = L.off_col + sizeof(int4) * (size_t)L.rows * L.n_kt;
+  size_t doc = (mask_kind == FLEXATTN_MASK_DOCUMENT) ? sizeof(int2) * (size_t)batch * L.n_t : 0;
+  L.bytes = (L.off_doc + doc + 255) & ~(size_t)255;
+  return L;
+}
+
+// Device-side view of a problem: what the kernels need, already resolved by the host.
+struct DevParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  const void* d_o;
+  void* dq;
+  void* dk;
+  void* dv;
+  float* l;
+  float* m;
+  float* delta;
+  const int32_t* doc_ids;
+  const float* alibi_slopes;
+  const int4* row_map;  // [rows][n_qt]
+  const int4* col_map;  // [rows][n_kt]
+  int32_t* status;
+  int batch, heads, seq_q, seq_k, head_dim;
+  int n_qt, n_kt, map_rows, doc_stride;
+  int window, stride;
+  float sm_scale, cap;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Compile-time mask functors.  True = keep.  di/dj are the document ids of positions i/j (only read
+// by the document mask).
+// ---------------------------------------------------------------------------------------------
+template <int MK>
+__device__ __forceinline__ bool mask_keep(int i, int j, int window, int stride, int di, int dj) {
+  if constexpr (MK == FLEXATTN_MASK_NONE) {
+    return true;
+  } else if constexpr (MK == FLEXATTN_MASK_CAUSAL) {
+    return i >= j;
+  } else if constexpr (MK == FLEXATTN_MASK_SLIDING_WINDOW) {
+    return (i - j) < window;
+  } else if constexpr (MK == FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL) {
+    return (unsigned)(i - j) < (unsigned)window;
+  } else if constexpr (MK == FLEXATTN_MASK_DOCUMENT) {
+    return (i >= j) && (di == dj);
+  } else {  // S2
+    return ((unsigned)(i - j) < (unsigned)window) || ((i >= j) && (j % stride == 0));
+  }
+}
+
+// Compile-time score functors on the scaled score s = sm_scale * <q,k>, natural units.
+// score_fwd returns t = score_mod(s) + bias(i, j); score_dsig returns d score_mod / d s.
+template <int SK>
+__device__ __forceinline__ float score_fwd(float s, int i, int j, float slope, float cap, float inv_cap) {
+  if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
+    return s - slope * (float)(i - j);
+  } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+    return cap * tanhf(s * inv_cap);
+  } else {
+    return s;
+  }
+}
+template <int SK>
+__device__ __forceinline__ float score_dsig(float s, float inv_cap) {
+  if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+    float th = tanhf(s * inv_cap);
+    return 1.0f - th * th;
+  } else {
+    return 1.0f;
+  }
+}
+
+__device__ __forceinline__ void report_timeout(int32_t* status, int kernel_id, int detail) {
+  if (status != nullptr) {
+    if (atomicCAS(status, 0, (int)FLEXATTN_ERR_TIMEOUT) == 0) {
+      status[1] = kernel_id;
+      status[2] = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+      status[3] = detail;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Launchers implemented by the kernel translation units; each returns a cudaError_t.
+// ---------------------------------------------------------------------------------------------
+cudaError_t launch_mask_map(cudaStream_t st, const FlexAttnParams& p);
+cudaError_t launch_delta(cudaStream_t st, const FlexAttnParams& p);
+cudaError_t launch_simt_fwd(cudaStream_t st, const DevParams& d, int dtype, int score, int mask);
+cudaError_t launch_simt_dq(cudaStream_t st, const DevParams& d, int dtype, int score, int mask);
+cudaError_t launch_simt_dkv(cudaStream_t st, const DevParams& d, int dtype, int score, int mask);
+// tensor-core (tcgen05) kernels: bf16, D in {64,128}
+int launch_sm100_fwd(cudaStream_t st, const DevParams& d, int score, int mask);
+int launch_sm100_dq(cudaStream_t st, const DevParams& d, int score, int mask);
+int launch_sm100_dkv(cudaStream_t st, const DevParams& d, int score, int mask);
+
+}  // namespace flexattn

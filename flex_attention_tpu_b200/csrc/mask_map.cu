@@ -1,0 +1,146 @@
+// Block-sparse mask-map builder.
+//
+// Replaces the reference's per-grid-step `block_mask_fn(q_blk, k_blk)` predicates (masks.py:20-28,
+// 63-81,113-139,161-177): instead of asking "does this tile pair run?" at every grid step, the map
+// stores, once per (mask, shape[, batch row]), for every q tile the contiguous range of kv tiles that
+// hold at least one kept pair and the contiguous sub-range whose pairs are ALL kept (the attention
+// kernels skip the mask functor there); and the transposed information for every kv tile.
+//
+// Tile classification is closed form on tile bounds; the document mask first reduces the ids of every
+// tile to (min, max).  A pair range that is only *possibly* non-empty (document ids that are not
+// sorted) is listed as a partial tile, which is always safe: partial tiles evaluate the exact mask.
+#include "common.cuh"
+
+namespace flexattn {
+namespace {
+
+struct PairClass {
+  bool any, all;
+};
+
+// q rows [q0,q1], keys [k0,k1] (inclusive, already clipped to the sequence lengths).
+__device__ __forceinline__ PairClass classify(int kind, int q0, int q1, int k0, int k1, int window,
+                                              int stride, int2 qd, int2 kd) {
+  PairClass c;
+  const int dmin = q0 - k1, dmax = q1 - k0;  // range of i - j over the tile pair
+  switch (kind) {
+    case FLEXATTN_MASK_NONE:
+      c.any = true; c.all = true; break;
+    case FLEXATTN_MASK_CAUSAL:
+      c.any = dmax >= 0; c.all = dmin >= 0; break;
+    case FLEXATTN_MASK_SLIDING_WINDOW:
+      c.any = dmin < window; c.all = dmax < window; break;
+    case FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL:
+      c.any = dmax >= 0 && dmin < window; c.all = dmin >= 0 && dmax < window; break;
+    case FLEXATTN_MASK_DOCUMENT: {
+      int lo = qd.x > kd.x ? qd.x : kd.x, hi = qd.y < kd.y ? qd.y : kd.y;
+      c.any = dmax >= 0 && lo <= hi;
+      c.all = dmin >= 0 && qd.x == qd.y && kd.x == kd.y && qd.x == kd.x;
+      break;
+    }
+    default: {  // S2: window-causal OR (key on the stride grid AND causal)
+      bool win_any = dmax >= 0 && dmin < window;
+      int first = ((k0 + stride - 1) / stride) * stride;  // first strided key in the tile
+      int lim = k1 < q1 ? k1 : q1;
+      c.any = win_any || (first <= lim);
+      c.all = dmin >= 0 && (dmax < window || stride == 1);
+      break;
+    }
+  }
+  return c;
+}
+
+__global__ void doc_minmax_kernel(const int32_t* __restrict__ doc_ids, int2* __restrict__ out, int n_t,
+                                  int len) {
+  // grid (n_t, B), block 128: (min,max) document id of positions [t*128, t*128+128) of batch row b
+  const int t = blockIdx.x, b = blockIdx.y;
+  const int pos = t * kTile + threadIdx.x;
+  int lo = INT32_MAX, hi = INT32_MIN;
+  if (pos < len) lo = hi = doc_ids[(size_t)b * len + pos];
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) {
+    lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, s));
+    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, s));
+  }
+  __shared__ int slo[4], shi[4];
+  if ((threadIdx.x & 31) == 0) { slo[threadIdx.x >> 5] = lo; shi[threadIdx.x >> 5] = hi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 4; ++w) { lo = min(lo, slo[w]); hi = max(hi, shi[w]); }
+    out[(size_t)b * n_t + t] = make_int2(lo, hi);
+  }
+}
+
+__global__ void mask_map_kernel(MapHeader hdr, MapHeader* __restrict__ hdr_out, int4* __restrict__ row_map,
+                                int4* __restrict__ col_map, const int2* __restrict__ docmm, int n_t) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) *hdr_out = hdr;
+  // one thread per (map row, tile) for the row map, then for the column map
+  const int n_row_entries = hdr.rows * hdr.n_qt;
+  const int n_col_entries = hdr.rows * hdr.n_kt;
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < n_row_entries + n_col_entries;
+       e += gridDim.x * blockDim.x) {
+    const bool is_col = e >= n_row_entries;
+    const int idx = is_col ? e - n_row_entries : e;
+    const int n_self = is_col ? hdr.n_kt : hdr.n_qt;
+    const int n_other = is_col ? hdr.n_qt : hdr.n_kt;
+    const int r = idx / n_self, t = idx % n_self;
+    const int len_self = is_col ? hdr.seq_k : hdr.seq_q;
+    const int len_other = is_col ? hdr.seq_q : hdr.seq_k;
+    const int s0 = t * kTile, s1 = min(s0 + kTile, len_self) - 1;
+    const int2 none = make_int2(0, 0);
+    const int2 sd = docmm ? docmm[(size_t)r * n_t + t] : none;
+    int lo = -1, hi = -1, flo = -1, fhi = -1;
+    bool run_open = false;
+    for (int u = 0; u < n_other; ++u) {
+      const int o0 = u * kTile, o1 = min(o0 + kTile, len_other) - 1;
+      const int2 od = docmm ? docmm[(size_t)r * n_t + u] : none;
+      PairClass c = is_col ? classify(hdr.mask_kind, o0, o1, s0, s1, hdr.window, hdr.stride, od, sd)
+                           : classify(hdr.mask_kind, s0, s1, o0, o1, hdr.window, hdr.stride, sd, od);
+      // a ragged tile on either side still needs its out-of-range positions masked
+      if (o0 + kTile > len_other) c.all = false;
+      if (c.any) {
+        if (lo < 0) lo = u;
+        hi = u + 1;
+      }
+      if (c.any && c.all) {
+        if (flo < 0) { flo = u; fhi = u + 1; run_open = true; }
+        else if (run_open && fhi == u) fhi = u + 1;
+      } else if (flo >= 0) {
+        run_open = false;
+      }
+    }
+    if (lo < 0) { lo = hi = 0; }
+    if (flo < 0) { flo = fhi = lo; }
+    (is_col ? col_map : row_map)[idx] = make_int4(lo, hi, flo, fhi);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_mask_map(cudaStream_t st, const FlexAttnParams& p) {
+  MapLayout L = map_layout(p.batch, p.seq_q, p.seq_k, p.mask_kind);
+  char* ws = static_cast<char*>(p.workspace);
+  MapHeader hdr{};
+  hdr.magic = kMapMagic;
+  hdr.mask_kind = p.mask_kind;
+  hdr.window = p.window;
+  hdr.stride = p.stride > 0 ? p.stride : 1;
+  hdr.seq_q = p.seq_q;
+  hdr.seq_k = p.seq_k;
+  hdr.n_qt = L.n_qt;
+  hdr.n_kt = L.n_kt;
+  hdr.rows = L.rows;
+  int2* docmm = nullptr;
+  if (p.mask_kind == FLEXATTN_MASK_DOCUMENT) {
+    docmm = reinterpret_cast<int2*>(ws + L.off_doc);
+    const int len = p.seq_q > p.seq_k ? p.seq_q : p.seq_k;
+    doc_minmax_kernel<<<dim3(L.n_t, p.batch), 128, 0, st>>>(p.doc_ids, docmm, L.n_t, len);
+  }
+  const int entries = L.rows * (L.n_qt + L.n_kt);
+  const int blocks = (entries + 127) / 128;
+  mask_map_kernel<<<blocks < 1184 ? blocks : 1184, 128, 0, st>>>(
+      hdr, reinterpret_cast<MapHeader*>(ws), reinterpret_cast<int4*>(ws + L.off_row), reinterpret_cast<int4*>(ws + L.off_col), docmm, L.n_t);
+  return cudaGetLastError();
+}
+
+}  // namespace flexattn

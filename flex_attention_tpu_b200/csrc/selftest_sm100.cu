@@ -1,0 +1,147 @@
+// Single-tile tensor-core self checks: the smallest kernels that exercise exactly the operand
+// staging the attention kernels rely on (TMA 128-byte swizzle -> tcgen05.mma descriptors, bf16 A
+// operand in tensor memory, MN-major B operand).  The test-suite compares them with a host matmul.
+#include "sm100.cuh"
+
+namespace flexattn {
+namespace {
+
+struct Tuning {
+  int lbo, sbo, kstep;
+};
+
+__global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ CUtensorMap tm_a,
+                                                       const __grid_constant__ CUtensorMap tm_b,
+                                                       const __nv_bfloat16* __restrict__ a_glob,
+                                                       float* __restrict__ d_out, int variant, int kdim,
+                                                       Tuning tune, int32_t* status, int* abort_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;                      // 2 panels x 16 KB
+  uint8_t* sB = smem + 2 * ptx::kPanelBytes;
+  uint64_t* bar_load = reinterpret_cast<uint64_t*>(smem + 4 * ptx::kPanelBytes);
+  uint64_t* bar_mma = bar_load + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_load + 2);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  constexpr uint32_t kCols = 256;
+
+  if (tid == 0) {
+    ptx::mbar_init(bar_load, 1);
+    ptx::mbar_init(bar_mma, 1);
+    ptx::fence_barrier_init();
+  }
+  if (warp == 0) {
+    ptx::tmem_alloc(tmem_slot, kCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t tD = 0, tA = 128;  // column offsets
+  const int panels = kdim / 64;
+  bool ok = true;
+
+  if (tid == 0) {
+    const uint32_t bytes = (uint32_t)(variant == 0 ? 2 * panels : 2) * ptx::kPanelBytes;
+    ptx::mbar_arrive_expect_tx(bar_load, bytes);
+    if (variant == 0) {
+      for (int p = 0; p < panels; ++p) {
+        ptx::tma_load_3d(sA + p * ptx::kPanelBytes, &tm_a, bar_load, p * 64, 0, 0);
+        ptx::tma_load_3d(sB + p * ptx::kPanelBytes, &tm_b, bar_load, p * 64, 0, 0);
+      }
+    } else {
+      for (int p = 0; p < 2; ++p) ptx::tma_load_3d(sB + p * ptx::kPanelBytes, &tm_b, bar_load, p * 64, 0, 0);
+    }
+  }
+  if (variant == 1) {
+    // stage A row `tid` into tensor memory as packed bf16 pairs (element k -> column k/2, low half = even k)
+    const uint32_t* row = reinterpret_cast<const uint32_t*>(a_glob + (size_t)tid * kdim);
+    for (int c0 = 0; c0 < kdim / 2; c0 += 32) {
+      uint32_t r[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) r[c] = row[c0 + c];
+      ptx::tmem_st32(lane_base + tA + c0, r);
+    }
+    ptx::tmem_wait_st();
+    ptx::tc_fence_before();
+  }
+  __syncthreads();
+  if (tid == 0) {
+    ok = ptx::mbar_wait(bar_load, 0);
+    if (ok) {
+      ptx::tc_fence_after();
+      const int ksteps = kdim / 16;
+      if (variant == 0) {
+        const uint32_t idesc = ptx::make_idesc(128, 128, false);
+        const uint32_t lbo = tune.lbo > 0 ? tune.lbo : 16, sbo = tune.sbo > 0 ? tune.sbo : 1024;
+        const uint32_t kstep = tune.kstep > 0 ? tune.kstep : 32;
+        for (int kk = 0; kk < ksteps; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * ptx::kPanelBytes + (uint32_t)(kk & 3) * kstep;
+          ptx::mma_ss(tmem + tD, ptx::make_smem_desc(ptx::smem_u32(sA) + off, lbo, sbo),
+                      ptx::make_smem_desc(ptx::smem_u32(sB) + off, lbo, sbo), idesc, kk > 0);
+        }
+      } else {
+        const uint32_t idesc = ptx::make_idesc(128, 128, true);
+        const uint32_t lbo = tune.lbo > 0 ? tune.lbo : ptx::kPanelBytes, sbo = tune.sbo > 0 ? tune.sbo : 1024;
+        const uint32_t kstep = tune.kstep > 0 ? tune.kstep : 2048;
+        for (int kk = 0; kk < ksteps; ++kk)
+          ptx::mma_ts(tmem + tD, tmem + tA + kk * 8, ptx::make_smem_desc(ptx::smem_u32(sB) + kk * kstep, lbo, sbo),
+                      idesc, kk > 0);
+      }
+      ptx::mma_commit(bar_mma);
+    } else {
+      give_up(abort_flag, status, 100, 1);
+    }
+  }
+  __syncwarp();
+  if (ptx::mbar_wait(bar_mma, 0)) {
+    ptx::tc_fence_after();
+#pragma unroll 1
+    for (int c0 = 0; c0 < 128; c0 += 32) {
+      uint32_t r[32];
+      ptx::tmem_ld32(lane_base + tD + c0, r);
+      ptx::tmem_wait_ld();
+      ptx::tmem_ld_acquire(r);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) d_out[(size_t)tid * 128 + c0 + c] = __uint_as_float(r[c]);
+    }
+  } else {
+    give_up(abort_flag, status, 100, 2);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, kCols);
+  }
+}
+
+}  // namespace
+}  // namespace flexattn
+
+using namespace flexattn;
+
+extern "C" int flexattn_selftest_umma(void* stream, int variant, const void* a, const void* b, float* d, int32_t kdim,
+                                      int32_t* status, const int32_t* tuning) {
+  if (a == nullptr || b == nullptr || d == nullptr) return FLEXATTN_ERR_NULL_POINTER;
+  if ((variant != 0 && variant != 1) || (kdim != 64 && kdim != 128)) return FLEXATTN_ERR_BAD_SHAPE;
+  CUtensorMap tm_a, tm_b;
+  int e = make_tile_map(&tm_a, a, 1, 128, kdim);  // [128, K] (only read through TMA by variant 0)
+  if (e) return e;
+  e = variant == 0 ? make_tile_map(&tm_b, b, 1, 128, kdim) : make_tile_map(&tm_b, b, 1, kdim, 128);
+  if (e) return e;
+  Tuning t{0, 0, 0};
+  if (tuning != nullptr) t = Tuning{tuning[0], tuning[1], tuning[2]};
+  const size_t smem = 4 * ptx::kPanelBytes + 1024 + 64;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return FLEXATTN_ERR_CUDA;
+    attr_set = true;
+  }
+  selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
+      tm_a, tm_b, static_cast<const __nv_bfloat16*>(a), d, variant, kdim, t, status, abort_flag_ptr());
+  return cudaGetLastError() == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;
+}

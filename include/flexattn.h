@@ -1,0 +1,167 @@
+/*
+ * flexattn.h -- C ABI of libflexattn.so: flex attention (score_mod + mask) for NVIDIA B200 (sm_100a).
+ *
+ * The reference project (james-zhengql/flex_attention_tpu) has no FFI of its own: its API is three
+ * Python functions, each wrapping one pl.pallas_call.  Every entry point below names the reference
+ * interface it replaces (file:line within that project).  A JAX host would bind these symbols as XLA
+ * FFI custom calls; this repository binds them with ctypes.
+ *
+ * Rules that hold for every entry point unless its comment says otherwise:
+ *   - plain pointers and sizes only; no C++ types, no exceptions cross the boundary;
+ *   - all tensor pointers are DEVICE pointers to contiguous row-major [B,H,S,D] (q,k,v,o,do,dq,dk,dv)
+ *     or [B,H,S] float (l,m,delta) arrays, 16-byte aligned;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*); the host is never synchronised
+ *     and nothing is allocated: outputs and the workspace belong to the caller;
+ *   - the return value is a FlexAttnStatus (0 = OK); launch-time CUDA errors are reported as
+ *     FLEXATTN_ERR_CUDA, asynchronous device-side time-outs through the optional `status` words.
+ *
+ * Fixed math convention (identical to the reference whenever sm_scale == 1, the only setting its
+ * score_fn tests use):
+ *     s = sm_scale * <q_i, k_j>;  t = score_mod(s) + bias(i, j);  x = keep(i, j) ? t : -inf
+ *     m_i = max_j x;  l_i = sum_j exp(x - m_i);  o_i = sum_j exp(x - m_i) / l_i * v_j
+ */
+#ifndef FLEXATTN_H_
+#define FLEXATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FLEXATTN_ABI_VERSION 1
+#define FLEXATTN_TILE 128 /* q-tile and kv-tile edge used by the mask map and by every kernel */
+
+typedef enum FlexAttnStatus {
+  FLEXATTN_OK = 0,
+  FLEXATTN_ERR_NULL_POINTER = 1,
+  FLEXATTN_ERR_BAD_SHAPE = 2,
+  FLEXATTN_ERR_UNSUPPORTED_DTYPE = 3,
+  FLEXATTN_ERR_UNSUPPORTED_HEAD_DIM = 4,
+  FLEXATTN_ERR_MISALIGNED = 5,
+  FLEXATTN_ERR_WORKSPACE_TOO_SMALL = 6,
+  FLEXATTN_ERR_UNSUPPORTED_MOD = 7,
+  FLEXATTN_ERR_CUDA = 8,
+  FLEXATTN_ERR_TIMEOUT = 9,
+  FLEXATTN_ERR_UNSUPPORTED_BACKEND = 10
+} FlexAttnStatus;
+
+typedef enum FlexAttnDType { FLEXATTN_BF16 = 0, FLEXATTN_F32 = 1 } FlexAttnDType;
+
+/* score_mod kinds: reference scores.py:3-11 (ALiBi demo; here real ALiBi with per-head slopes and
+ * global distance, bias = -slope_h * (i - j)) and scores.py:13-18 (tanh soft cap). */
+typedef enum FlexAttnScoreKind {
+  FLEXATTN_SCORE_NONE = 0,
+  FLEXATTN_SCORE_ALIBI = 1,
+  FLEXATTN_SCORE_SOFTCAP = 2
+} FlexAttnScoreKind;
+
+/* mask kinds (keep predicate): reference masks.py:3-6 (none), :15-16 (causal, i >= j),
+ * :45-59 (sliding window, i - j < W, NOT causal), window AND causal (0 <= i - j < W,
+ * mha_reference.py:59-62 with :80-94), :105-110 (document: same id AND causal),
+ * :146-158 (S2: window-causal OR (j % stride == 0 AND causal)). */
+typedef enum FlexAttnMaskKind {
+  FLEXATTN_MASK_NONE = 0,
+  FLEXATTN_MASK_CAUSAL = 1,
+  FLEXATTN_MASK_SLIDING_WINDOW = 2,
+  FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL = 3,
+  FLEXATTN_MASK_DOCUMENT = 4,
+  FLEXATTN_MASK_S2 = 5
+} FlexAttnMaskKind;
+
+typedef enum FlexAttnBackend {
+  FLEXATTN_BACKEND_AUTO = 0,    /* bf16 with D in {64,128}: tcgen05 kernels; otherwise SIMT */
+  FLEXATTN_BACKEND_SIMT = 1,    /* fp32-accurate CUDA-core kernels (any dtype, D in {32,64,128}) */
+  FLEXATTN_BACKEND_TCGEN05 = 2  /* fail with UNSUPPORTED_BACKEND instead of falling back */
+} FlexAttnBackend;
+
+typedef struct FlexAttnParams {
+  /* tensors (device) */
+  const void* q;     /* [B,H,Sq,D] */
+  const void* k;     /* [B,H,Sk,D] */
+  const void* v;     /* [B,H,Sk,D] */
+  void* o;           /* [B,H,Sq,D]  written by fwd; read by bwd_preprocess */
+  const void* d_o;   /* [B,H,Sq,D]  upstream gradient */
+  void* dq;          /* [B,H,Sq,D] */
+  void* dk;          /* [B,H,Sk,D] */
+  void* dv;          /* [B,H,Sk,D] */
+  float* l;          /* [B,H,Sq]  sum_j exp(x - m)   (fwd output, bwd input) */
+  float* m;          /* [B,H,Sq]  row max of x       (fwd output, bwd input) */
+  float* delta;      /* [B,H,Sq]  rowsum(o * do)     (bwd_preprocess output, dq/dkv input) */
+  const int32_t* doc_ids;     /* [B, max(Sq,Sk)] document id per position; MASK_DOCUMENT only */
+  const float* alibi_slopes;  /* [H]; SCORE_ALIBI only */
+  /* problem */
+  int32_t batch, heads, seq_q, seq_k, head_dim;
+  int32_t dtype;              /* FlexAttnDType of q,k,v,o,do,dq,dk,dv */
+  float sm_scale;
+  int32_t score_kind;         /* FlexAttnScoreKind */
+  float softcap;              /* cap of SCORE_SOFTCAP */
+  int32_t mask_kind;          /* FlexAttnMaskKind */
+  int32_t window;             /* W of the window masks and of S2 */
+  int32_t stride;             /* stride of S2 */
+  /* caller-owned scratch: holds the mask map written by flexattn_build_mask_map */
+  void* workspace;
+  size_t workspace_bytes;
+  /* optional device int32[4]: {code, kernel id, block, detail}; written when a bounded wait inside a
+   * kernel gives up (code = FLEXATTN_ERR_TIMEOUT).  Zero it before the call; may be NULL. */
+  int32_t* status;
+  int32_t backend;            /* FlexAttnBackend */
+  int32_t reserved;
+} FlexAttnParams;
+
+/* ABI version of the loaded library (== FLEXATTN_ABI_VERSION of the header it was built from). */
+int flexattn_abi_version(void);
+
+/* Human-readable name of a FlexAttnStatus.  Never NULL. */
+const char* flexattn_status_string(int status);
+
+/* Bytes of workspace the mask map needs for this problem (depends on batch, seq_q, seq_k, mask_kind).
+ * Replaces nothing in the reference (its block_mask_fn closures are evaluated inside the grid,
+ * flex_attention_kernel.py:97-106,231-236); returns 0 on invalid params. */
+size_t flexattn_workspace_bytes(const FlexAttnParams* p);
+
+/* Block-sparse mask-map builder.  Replaces the per-grid-step `block_mask_fn(q_blk, k_blk)` closures of
+ * masks.py:20-28,63-81,113-139,161-177 and the "fetch block 0 instead" redirect of
+ * flex_attention_kernel.py:97-106: for every q tile (and every kv tile, for the dk/dv kernel) it writes
+ * the contiguous range of opposite-side tiles holding at least one kept pair, and the sub-range that
+ * is entirely kept (no mask evaluation needed there).  Must run (on the same stream, or ordered before)
+ * ahead of fwd / bwd_dq / bwd_dkv for the same mask, shapes and doc_ids. */
+int flexattn_build_mask_map(void* stream, const FlexAttnParams* p);
+
+/* Forward.  Replaces `_flex_attention_impl` (flex_attention_kernel.py:66-193) with
+ * save_residuals=True: writes o, l, m. */
+int flexattn_fwd(void* stream, const FlexAttnParams* p);
+
+/* delta = rowsum(o * do).  Replaces the host-side `jnp.sum(o * do, -1)` every reference call site does
+ * before the backward kernels (flex_attention_dq_bwd.py:697,932). */
+int flexattn_bwd_preprocess(void* stream, const FlexAttnParams* p);
+
+/* dQ.  Replaces `flex_attention_bwd_dq` (flex_attention_dq_bwd.py:114-267).  Reads q,k,v,do,l,m,delta. */
+int flexattn_bwd_dq(void* stream, const FlexAttnParams* p);
+
+/* dK and dV.  Replaces `flash_attention_bwd_dkv` (flex_attention_dkv_kernel.py:23-174 and its
+ * mask-aware twin flash_attention_dkv_bwd.py:27-180).  Reads q,k,v,do,l,m,delta. */
+int flexattn_bwd_dkv(void* stream, const FlexAttnParams* p);
+
+/* Decodes the mask map in `workspace` for tests and tools: copies entry `index` of the row map
+ * (which = 0: per q tile) or column map (which = 1: per kv tile) of batch row `b` into out[4] =
+ * {first tile, end tile (exclusive), first fully-kept tile, end of fully-kept run}.  Synchronises
+ * `stream`.  Replaces nothing in the reference. */
+int flexattn_read_mask_map(void* stream, const FlexAttnParams* p, int which, int b, int index,
+                           int32_t out[4]);
+
+/* Single-tile tensor-core self checks used by the test-suite (not part of the attention path):
+ * D[128,128] = A[128,K] * B^T with A,B bf16 in global memory; `variant` selects the operand
+ * staging: 0 = A,B K-major from shared memory; 1 = A from tensor memory (bf16 packed), B MN-major
+ * from shared memory (then B is [K,128] row-major).  kdim is 64 or 128.  Output f32 [128,128].
+ * `tuning` (host pointer, may be NULL) overrides descriptor fields for hardware probing:
+ * {leading byte offset, stride byte offset, bytes added to the start address per K step, unused};
+ * a value <= 0 keeps the library's own setting.  Replaces nothing in the reference. */
+int flexattn_selftest_umma(void* stream, int variant, const void* a, const void* b, float* d,
+                           int32_t kdim, int32_t* status, const int32_t* tuning);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLEXATTN_H_ */

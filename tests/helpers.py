@@ -1,0 +1,105 @@
+"""Shared helpers of the GPU parity tests: seeded inputs, mask/score construction in the package's
+vocabulary, one call of the whole hot path through the Python entry points, and the error metrics."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from oracle import mha_reference_cpu as oracle
+
+# tolerances fixed by the build's brief: fp32 inputs max-abs <= 2e-3; bf16 inputs max-abs <= 2e-2 and
+# max-relative (max-abs error / max-abs reference) <= 1e-2, on O, dQ, dK, dV
+TOL = {torch.float32: dict(abs=2e-3, rel=None), torch.bfloat16: dict(abs=2e-2, rel=1e-2)}
+
+
+def make_qkvdo(shape_q, shape_k, seed, dtype, device="cuda"):
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal(shape_q, dtype=np.float32)
+    k = rng.standard_normal(shape_k, dtype=np.float32)
+    v = rng.standard_normal(shape_k, dtype=np.float32)
+    do = rng.standard_normal(shape_q, dtype=np.float32)
+    ts = [torch.from_numpy(a).to(dtype) for a in (q, k, v, do)]
+    host = [t.float().numpy() for t in ts]     # what the oracle sees: the rounded values, up-cast
+    return [t.to(device) for t in ts], host
+
+
+def build_mods(fa, mask_kind, score_kind, *, window=0, stride=0, doc_ids=None, cap=0.0, slopes=None):
+    """(mask_fn, block_mask_fn, score_fn, segment_ids) in the package's vocabulary."""
+    M = fa.masks
+    seg = None
+    if mask_kind == "none":
+        mf, bf = M.place_holder(128, 128)
+    elif mask_kind == "causal":
+        mf, bf = M.make_causal_mask_fns(128, 128)
+    elif mask_kind == "sliding_window":
+        mf, bf = M.make_sliding_window_mask_fns(128, 128, window)
+    elif mask_kind == "sliding_window_causal":
+        mf, bf = M.make_sliding_window_mask_fns(128, 128, window, causal=True)
+    elif mask_kind == "s2":
+        mf, bf = M.make_s2_mask_fns(128, 128, window, stride)
+    elif mask_kind == "document":
+        mf, bf, seg = None, None, torch.as_tensor(doc_ids)
+    else:
+        raise ValueError(mask_kind)
+    sf = None
+    if score_kind == "alibi":
+        sf = fa.scores.make_alibi_score_fn(slopes)
+    elif score_kind == "softcap":
+        sf = fa.scores.make_softcap_score_fn(cap)
+    return mf, bf, sf, seg
+
+
+def run_hot_path(fa, q, k, v, do, *, sm_scale, mask_kind="none", score_kind="none", backend="auto", window=0,
+                 stride=0, doc_ids=None, cap=0.0, slopes=None, status=None):
+    """fwd -> delta -> dq -> dkv through the reference-named entry points.  Returns a dict of tensors."""
+    mf, bf, sf, seg = build_mods(fa, mask_kind, score_kind, window=window, stride=stride, doc_ids=doc_ids,
+                                 cap=cap, slopes=slopes)
+    o, l, m = fa._flex_attention_impl(q, k, v, None, seg, True, False, sm_scale, 1, 128, 128, 128, False, bf, mf,
+                                      sf, backend=backend, status=status)
+    delta = fa.bwd_preprocess(o, do)
+    dq = fa.flex_attention_bwd_dq(q, k, v, None, seg, l, m, o, do, delta, block_b=1, block_q=128,
+                                  block_k_major=128, block_k=128, sm_scale=sm_scale, debug=False, score_fn=sf,
+                                  mask_fn=mf, block_mask_fn=bf, backend=backend, status=status)
+    dk, dv = fa.flash_attention_bwd_dkv(k, v, q, None, seg, l, m, delta, do, block_b=1, block_q=128,
+                                        block_q_major=128, block_k_major=128, block_k=128, sm_scale=sm_scale,
+                                        causal=False, debug=False, score_fn=sf, mask_fn=mf, block_mask_fn=bf,
+                                        backend=backend, status=status)
+    torch.cuda.synchronize()
+    return dict(o=o, l=l, m=m, delta=delta, dq=dq, dk=dk, dv=dv)
+
+
+def oracle_hot_path(qh, kh, vh, doh, *, sm_scale, mask_kind="none", score_kind="none", window=None, stride=None,
+                    doc_ids=None, cap=None, slopes=None):
+    kw = dict(sm_scale=sm_scale, mask_kind=mask_kind, window=window, stride=stride, doc_ids=doc_ids,
+              score_kind=score_kind, cap=cap, alibi_slopes=slopes)
+    o, l, m = oracle.mha_reference(qh, kh, vh, save_residuals=True, **kw)
+    dq, dk, dv = oracle.mha_bwd_reference(qh, kh, vh, o, doh, l, m, **kw)
+    return dict(o=o, l=l, m=m, delta=oracle.delta_reference(o, doh), dq=dq, dk=dk, dv=dv)
+
+
+def errors(test, ref):
+    t = test.detach().float().cpu().numpy() if isinstance(test, torch.Tensor) else np.asarray(test, np.float32)
+    r = np.asarray(ref, np.float32)
+    diff = np.abs(t - r)
+    return dict(max_abs=float(diff.max()), max_rel=float(diff.max() / max(np.abs(r).max(), 1e-30)),
+                rel_l2=float(np.linalg.norm(t - r) / (np.linalg.norm(r) + 1e-6)))
+
+
+def assert_close(got, want, dtype, names=("o", "dq", "dk", "dv"), what=""):
+    tol = TOL[dtype]
+    report = {}
+    for n in names:
+        e = errors(got[n], want[n])
+        report[n] = e
+        assert np.isfinite(e["max_abs"]), f"{what} {n}: non-finite result"
+        assert e["max_abs"] <= tol["abs"], f"{what} {n}: max-abs {e['max_abs']:.3e} > {tol['abs']}  ({e})"
+        if tol["rel"] is not None:
+            assert e["max_rel"] <= tol["rel"], f"{what} {n}: max-rel {e['max_rel']:.3e} > {tol['rel']}  ({e})"
+    # residuals: l relative, m absolute (f32 in every dtype; the tensor-core path computes them from
+    # bf16 products, hence the looser bound there)
+    lm_tol = 2e-3 if dtype == torch.float32 else 2e-2
+    e_m = errors(got["m"], want["m"])
+    assert e_m["max_abs"] <= lm_tol, f"{what} m: {e_m}"
+    l_t, l_r = got["l"].float().cpu().numpy(), np.asarray(want["l"])
+    assert float(np.abs(l_t / l_r - 1).max()) <= lm_tol, f"{what} l: rel {np.abs(l_t / l_r - 1).max():.3e}"
+    return report

@@ -1,0 +1,122 @@
+"""Parity of the CUDA hot path (through the reference-named Python entry points and the C ABI) with
+(1) the committed fixtures produced by the reference's own mha_reference.py and (2) the CPU oracle on
+seeded inputs, for every mask kind x score kind, both dtypes, both backends, ragged sizes."""
+import numpy as np
+import pytest
+import torch
+
+from cases import CASES, make_inputs
+from golden_map import oracle_kwargs
+from helpers import TOL, assert_close, errors, make_qkvdo, oracle_hot_path, run_hot_path
+from oracle import mha_reference_cpu as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _fa():
+    import flex_attention_tpu_b200 as fa
+    return fa
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_float32_against_reference_vectors(name, golden):
+    """fp32 inputs, CUDA-core kernels, against the vectors the reference's mha_reference.py produced."""
+    fa = _fa()
+    c = CASES[name]
+    kw = oracle_kwargs(c)
+    q, k, v, do = (torch.from_numpy(a).cuda() for a in make_inputs(c))
+    got = run_hot_path(fa, q, k, v, do, sm_scale=kw["sm_scale"], mask_kind=kw.get("mask_kind", "none"),
+                       score_kind=kw.get("score_kind", "none"), window=kw.get("window", 0), stride=kw.get("stride", 0),
+                       doc_ids=kw.get("doc_ids"), cap=kw.get("cap", 0.0), slopes=kw.get("alibi_slopes"))
+    want = {n: golden[f"{name}/{n}"] for n in ("o", "l", "m")}
+    names = ["o"]
+    if not c.get("softcap"):
+        want.update({n: golden[f"{name}/{n}"] for n in ("dq", "dk", "dv")})
+        names += ["dq", "dk", "dv"]
+    assert_close(got, want, torch.float32, names=names, what=name)
+
+
+MASKS = {
+    "none": dict(),
+    "causal": dict(),
+    "sliding_window": dict(window=150),
+    "sliding_window_causal": dict(window=200),
+    "document": dict(),
+    "s2": dict(window=96, stride=32),
+}
+
+
+def _case(mask_kind, score_kind, dtype, B, H, Sq, Sk, D, seed, backend):
+    fa = _fa()
+    (q, k, v, do), host = make_qkvdo((B, H, Sq, D), (B, H, Sk, D), seed, dtype)
+    kw = dict(MASKS[mask_kind])
+    doc = None
+    if mask_kind == "document":
+        doc, _ = oracle.draw_documents(np.random.default_rng(seed), B, max(Sq, Sk), lo=60, hi=300)
+    slopes = oracle.alibi_slopes(H) if score_kind == "alibi" else None
+    cap = 4.0 if score_kind == "softcap" else None
+    sm_scale = 1.0 / np.sqrt(D)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    got = run_hot_path(fa, q, k, v, do, sm_scale=sm_scale, mask_kind=mask_kind, score_kind=score_kind,
+                       backend=backend, window=kw.get("window", 0), stride=kw.get("stride", 0), doc_ids=doc,
+                       cap=cap or 0.0, slopes=slopes, status=status)
+    assert status.tolist() == [0, 0, 0, 0], f"device-side wait gave up: {status.tolist()}"
+    want = oracle_hot_path(*host, sm_scale=sm_scale, mask_kind=mask_kind, score_kind=score_kind,
+                           window=kw.get("window"), stride=kw.get("stride"), doc_ids=doc, cap=cap, slopes=slopes)
+    e = errors(got["delta"], want["delta"])
+    assert e["max_abs"] <= (2e-3 if dtype == torch.float32 else 6e-2), f"delta {e}"
+    return assert_close(got, want, dtype, what=f"{mask_kind}/{score_kind}/{backend}/D{D}")
+
+
+@pytest.mark.parametrize("score_kind", ["none", "alibi", "softcap"])
+@pytest.mark.parametrize("mask_kind", sorted(MASKS))
+def test_simt_float32(mask_kind, score_kind):
+    _case(mask_kind, score_kind, torch.float32, 2, 2, 333, 333, 64, 101, "auto")
+
+
+@pytest.mark.parametrize("D", [32, 128])
+def test_simt_float32_head_dims_and_rectangular(D):
+    _case("none", "none", torch.float32, 1, 2, 200, 456, D, 102, "auto")
+    _case("causal", "softcap", torch.float32, 1, 2, 456, 456, D, 103, "simt")
+
+
+@pytest.mark.parametrize("score_kind", ["none", "alibi", "softcap"])
+@pytest.mark.parametrize("mask_kind", sorted(MASKS))
+def test_simt_bfloat16(mask_kind, score_kind):
+    _case(mask_kind, score_kind, torch.bfloat16, 1, 2, 300, 300, 128, 104, "simt")
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("score_kind", ["none", "alibi", "softcap"])
+@pytest.mark.parametrize("mask_kind", sorted(MASKS))
+def test_tensor_core_bfloat16(mask_kind, score_kind, D):
+    """The tcgen05 kernels: every mask x score functor, both head dims, ragged sequence (not a tile multiple)."""
+    _case(mask_kind, score_kind, torch.bfloat16, 2, 2, 777, 777, D, 105 + D, "tcgen05")
+
+
+@pytest.mark.parametrize("Sq,Sk", [(128, 128), (100, 100), (256, 1024), (1000, 384), (129, 257)])
+def test_tensor_core_shapes(Sq, Sk):
+    _case("none", "none", torch.bfloat16, 1, 3, Sq, Sk, 128, 300 + Sq, "tcgen05")
+    if Sq == Sk:
+        _case("causal", "none", torch.bfloat16, 1, 3, Sq, Sk, 128, 301 + Sq, "tcgen05")
+
+
+def test_tensor_core_is_deterministic():
+    fa = _fa()
+    (q, k, v, do), _ = make_qkvdo((1, 4, 1024, 128), (1, 4, 1024, 128), 9, torch.bfloat16)
+    a = run_hot_path(fa, q, k, v, do, sm_scale=0.088, mask_kind="causal", backend="tcgen05")
+    b = run_hot_path(fa, q, k, v, do, sm_scale=0.088, mask_kind="causal", backend="tcgen05")
+    for n in ("o", "l", "m", "dq", "dk", "dv"):
+        assert torch.equal(a[n], b[n]), n
+
+
+def test_tensor_core_matches_simt_on_long_rows():
+    """Longer rows than the oracle cases: the two GPU backends must agree (SIMT is the fp32-accurate one)."""
+    fa = _fa()
+    (q, k, v, do), _ = make_qkvdo((1, 2, 4096, 128), (1, 2, 4096, 128), 10, torch.bfloat16)
+    sm = 1.0 / np.sqrt(128)
+    a = run_hot_path(fa, q, k, v, do, sm_scale=sm, mask_kind="causal", backend="tcgen05")
+    b = run_hot_path(fa, q, k, v, do, sm_scale=sm, mask_kind="causal", backend="simt")
+    for n in ("o", "dq", "dk", "dv"):
+        e = errors(a[n], b[n].float().cpu().numpy())
+        assert e["max_abs"] <= TOL[torch.bfloat16]["abs"] and e["max_rel"] <= TOL[torch.bfloat16]["rel"], (n, e)
