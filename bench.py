@@ -1,0 +1,434 @@
+#!/usr/bin/env python
+"""Benchmark of the flex-attention hot path (forward + delta preprocess + dQ + dK/dV) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|t|c3|c4] [--impl ours|reference]
+
+One "step" = one forward and one backward pass of the hot path over one batch of synthetic input.
+Prints ONE JSON line (rank 0): the metric is causal-adjusted attention TFLOP/s = kept-pair FLOPs
+(fwd 4*B*H*D*pairs + bwd 10*B*H*D*pairs) / time, whole job over all GPUs.  With N > 1 every rank
+runs the same per-GPU workload on its own (batch x head) shard (weak scaling, no collective on the
+data path; NCCL only for the barrier, the max-over-ranks time and the verification gather).
+
+`--impl reference` times the reference's CPU definition of the same path (the NumPy restatement in
+oracle/, because JAX is not installed) on the host cores, on a bounded sample of (batch, head) slices.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "fwd+bwd attention TFLOP/s (causal-adjusted)"
+
+# Per-GPU workloads.  c2 = BASELINE.json configs[1]; t = the S=8192, D=128 target point; c3 / c4 =
+# configs[2] / configs[3].
+WORKLOADS = {
+    "c2": dict(B=8, H=16, S=2048, D=128, seed=1, mask="causal", score="none",
+               desc="causal MHA fwd+bwd bf16 B=8 H=16 S=2048 D=128 (BASELINE configs[1])"),
+    "t": dict(B=4, H=32, S=8192, D=128, seed=5, mask="causal", score="none",
+              desc="causal MHA fwd+bwd bf16 B=4 H=32 S=8192 D=128 (target point)"),
+    "c3": dict(B=4, H=32, S=8192, D=128, seed=2, mask="sliding_window_causal", window=256, score="alibi",
+               desc="sliding-window(256, causal) + ALiBi fwd+bwd bf16 B=4 H=32 S=8192 D=128 (BASELINE configs[2])"),
+    "c4": dict(B=2, H=16, S=16384, D=128, seed=3, mask="document", score="softcap", cap=50.0,
+               desc="document mask + tanh softcap(50) fwd+bwd bf16 B=2 H=16 S=16384 D=128 (BASELINE configs[3])"),
+}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel on the c2 workload, from
+# the ncu capture summarised under profiles/ (None until a capture exists for the current kernel).
+NCU_TRAFFIC_BYTES = {"c2": None}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(tflops=float(d["bf16_tflops"]), tflops_sustained=float(d.get("bf16_tflops_sustained", 0)),
+                    hbm=float(d["hbm_gbs"]), source="measured")
+    return dict(tflops=1590.0, tflops_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+def pairs_per_bh(w, doc_ids=None):
+    from flex_attention_tpu_b200 import workloads
+    # list: one entry per batch row for document masks, else a single entry
+    return workloads.kept_pairs(w["mask"], w["S"], window=w.get("window", 0), stride=w.get("stride", 0),
+                                doc_ids=doc_ids)
+
+
+def total_pairs(w, doc_ids=None):
+    per_row = pairs_per_bh(w, doc_ids)
+    if len(per_row) == 1:
+        return per_row[0] * w["B"] * w["H"]
+    return sum(per_row) * w["H"]
+
+
+# ------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc, self.index = None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        return dict(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons),
+                    samples=len(sm))
+
+
+# ------------------------------------------------------------------------------------------ inputs
+def make_device_inputs(w, rank, torch):
+    """Synthetic q, k, v, do ~ N(0,1) in bf16, generated on the device from the workload seed (+ rank)."""
+    g = torch.Generator(device="cuda").manual_seed(w["seed"] * 1000 + rank)
+    shape = (w["B"], w["H"], w["S"], w["D"])
+    return [torch.randn(shape, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16) for _ in range(4)]
+
+
+def make_mods(w, fa, rank):
+    from flex_attention_tpu_b200 import workloads
+    seg = None
+    doc = None
+    if w["mask"] == "causal":
+        mf, bf = fa.masks.make_causal_mask_fns(128, 128)
+    elif w["mask"] == "sliding_window_causal":
+        mf, bf = fa.masks.make_sliding_window_mask_fns(128, 128, w["window"], causal=True)
+    elif w["mask"] == "document":
+        doc, _ = workloads.draw_documents(np.random.default_rng(w["seed"] * 1000 + rank), w["B"], w["S"])
+        mf, bf, seg = None, None, doc
+    else:
+        mf, bf = fa.masks.place_holder(128, 128)
+    sf = None
+    if w["score"] == "alibi":
+        sf = fa.scores.make_alibi_score_fn(fa.scores.alibi_slopes(w["H"]))
+    elif w["score"] == "softcap":
+        sf = fa.scores.make_softcap_score_fn(w["cap"])
+    return mf, bf, sf, seg, doc
+
+
+class HotPath:
+    """fwd + preprocess + dq + dkv through the package's reference-named entry points."""
+
+    def __init__(self, w, fa, torch, rank):
+        self.fa, self.torch, self.w = fa, torch, w
+        self.mf, self.bf, self.sf, seg, self.doc = make_mods(w, fa, rank)
+        self.seg = None if seg is None else torch.from_numpy(seg).cuda()
+        self.sm_scale = 1.0 / float(np.sqrt(w["D"]))
+
+    def fwd(self, q, k, v):
+        return self.fa._flex_attention_impl(q, k, v, None, self.seg, True, False, self.sm_scale, 1, 128, 128, 128,
+                                            False, self.bf, self.mf, self.sf)
+
+    def bwd(self, q, k, v, o, l, m, do):
+        fa = self.fa
+        delta = fa.bwd_preprocess(o, do)
+        dq = fa.flex_attention_bwd_dq(q, k, v, None, self.seg, l, m, o, do, delta, sm_scale=self.sm_scale,
+                                      score_fn=self.sf, mask_fn=self.mf, block_mask_fn=self.bf)
+        dk, dv = fa.flash_attention_bwd_dkv(k, v, q, None, self.seg, l, m, delta, do, sm_scale=self.sm_scale,
+                                            score_fn=self.sf, mask_fn=self.mf, block_mask_fn=self.bf)
+        return dq, dk, dv
+
+    def step(self, q, k, v, do):
+        o, l, m = self.fwd(q, k, v)
+        dq, dk, dv = self.bwd(q, k, v, o, l, m, do)
+        return o, dq, dk, dv
+
+
+def time_kernels(hp, q, k, v, do, torch, iters=5):
+    """Average device time of each kernel of the path, each timed alone with CUDA events on the launching
+    (current) stream."""
+    fa = hp.fa
+    o, l, m = hp.fwd(q, k, v)
+    delta = fa.bwd_preprocess(o, do)
+    calls = {
+        "fwd": lambda: hp.fwd(q, k, v),
+        "delta": lambda: fa.bwd_preprocess(o, do),
+        "dq": lambda: fa.flex_attention_bwd_dq(q, k, v, None, hp.seg, l, m, o, do, delta, sm_scale=hp.sm_scale,
+                                               score_fn=hp.sf, mask_fn=hp.mf, block_mask_fn=hp.bf),
+        "dkv": lambda: fa.flash_attention_bwd_dkv(k, v, q, None, hp.seg, l, m, delta, do, sm_scale=hp.sm_scale,
+                                                  score_fn=hp.sf, mask_fn=hp.mf, block_mask_fn=hp.bf),
+    }
+    out = {}
+    for name, fn in calls.items():
+        fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        out[name] = float(np.mean(ts))
+    return out
+
+
+# ------------------------------------------------------------------------------------------ CPU legs
+def cpu_reference_sample(w, budget_s=15.0, max_slices=None):
+    """Times the CPU restatement of mha_reference + mha_bwd_reference on (batch, head) slices of the
+    workload, one slice per host thread, for about `budget_s` seconds.  Returns (TFLOP/s, cores, text)."""
+    from oracle import mha_reference_cpu as oracle
+    try:
+        from threadpoolctl import threadpool_limits
+    except ImportError:  # pragma: no cover
+        threadpool_limits = None
+    cores = min(os.cpu_count() or 1, 32)
+    S, D = w["S"], w["D"]
+    rng = np.random.default_rng(w["seed"])
+    doc = None
+    if w["mask"] == "document":
+        doc, _ = oracle.draw_documents(rng, 1, S)
+    kw = dict(sm_scale=1.0 / np.sqrt(D), mask_kind=w["mask"], window=w.get("window"), doc_ids=doc,
+              score_kind=w["score"], cap=w.get("cap"), alibi_slopes=oracle.alibi_slopes(1))
+    pairs = oracle.kept_pairs(w["mask"], S, S, window=w.get("window"), doc_ids=doc)[0]
+
+    def one_slice(seed):
+        r = np.random.default_rng(seed)
+        q, k, v, do = (r.standard_normal((1, 1, S, D), dtype=np.float32) for _ in range(4))
+        o, l, m = oracle.mha_reference(q, k, v, save_residuals=True, **kw)
+        oracle.mha_bwd_reference(q, k, v, o, do, l, m, **kw)
+
+    def run(n):
+        t0 = time.perf_counter()
+        with ThreadPoolExecutor(cores) as ex:
+            list(ex.map(one_slice, range(n)))
+        return time.perf_counter() - t0
+
+    ctx = threadpool_limits(limits=1) if threadpool_limits else None
+    try:
+        t1 = run(cores)                       # one slice per thread: calibrates the sample size
+        n = int(max(cores, min(max_slices or 10 ** 9, cores * max(1, round(budget_s / max(t1, 1e-3))))))
+        t = run(n) if n > cores else t1
+        n = n if n > cores else cores
+    finally:
+        if ctx is not None:
+            ctx.__exit__(None, None, None)
+    flops = 14.0 * D * pairs * n
+    sample = f"{n} of {w['B'] * w['H']} (batch, head) slices of the workload, fwd+bwd, {t:.1f} s on {cores} threads"
+    return flops / t / 1e12, cores, sample, t / n
+
+
+def run_reference_arm(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step_budget = max(2.0, min(15.0, 120.0 / max(1, args.steps + args.warmup)))
+    vals, sample, cores = [], "", 1
+    for it in range(args.warmup + args.steps):
+        v, cores, sample, _ = cpu_reference_sample(w, budget_s=per_step_budget)
+        if it >= args.warmup:
+            vals.append(v)
+    value = float(np.mean(vals))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["desc"], "note": "CPU restatement of the reference's mha_reference / "
+                   "mha_bwd_reference (JAX is not installed, so the reference itself cannot run)"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------ main arm
+def run_ours(args, w):
+    import torch
+    import torch.distributed as dist
+    import flex_attention_tpu_b200 as fa
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    q, k, v, do = make_device_inputs(w, rank, torch)
+    hp = HotPath(w, fa, torch, rank)
+    pairs = total_pairs(w, hp.doc)
+    flops_fwd = 4.0 * w["D"] * pairs
+    flops_bwd = 10.0 * w["D"] * pairs
+
+    # ---- device-resident timing: W warm-up steps, K timed steps, CUDA events, max over ranks
+    for _ in range(args.warmup):
+        hp.step(q, k, v, do)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ef = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    e0.record()
+    for s in range(args.steps):
+        o, l, m = hp.fwd(q, k, v)
+        ef[s][0].record()
+        out = hp.bwd(q, k, v, o, l, m, do)
+        ef[s][1].record()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = max_over_ranks(e0.elapsed_time(e1))
+    ms_step = total_ms / args.steps
+    # split of the step into fwd / bwd (this rank)
+    fwd_ms, bwd_ms, prev = [], [], e0
+    for a, b_ in ef:
+        fwd_ms.append(prev.elapsed_time(a))
+        bwd_ms.append(a.elapsed_time(b_))
+        prev = b_
+    fwd_ms, bwd_ms = float(np.mean(fwd_ms)), float(np.mean(bwd_ms))
+    value = world * (flops_fwd + flops_bwd) / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the public entry points with HOST buffers (pinned): H2D of q,k,v,do and
+    # D2H of o,dq,dk,dv inside the timed region, every step
+    host_in = [t.cpu().pin_memory() for t in (q, k, v, do)]
+    host_out = [torch.empty_like(t).pin_memory() for t in host_in]
+    dev_in = [torch.empty_like(t) for t in (q, k, v, do)]
+
+    def e2e_step():
+        for d, h_ in zip(dev_in, host_in):
+            d.copy_(h_, non_blocking=True)
+        res = hp.step(*dev_in)
+        for h_, r in zip(host_out, res):
+            h_.copy_(r, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    g1.record()
+    barrier()
+    e2e_ms = max_over_ranks(g0.elapsed_time(g1)) / e2e_steps
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    e2e_value = world * (flops_fwd + flops_bwd) / (e2e_ms * 1e-3) / 1e12
+    io_bytes = sum(t.numel() * t.element_size() for t in host_in)
+
+    # ---- verification gather over NCCL (outside every timed region): per-rank checksums of the outputs
+    checks = None
+    if world > 1:
+        mine = torch.stack([t.float().abs().mean() for t in out] + [o.float().abs().mean()]).double()
+        allv = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allv, mine)
+        checks = [[float(x) for x in t.tolist()] for t in allv]
+
+    if rank == 0:
+        peaks = measured_peaks()
+        kt = time_kernels(hp, q, k, v, do, torch)
+        # executed-algorithmic FLOPs of each kernel: GEMMs it has to compute x kept pairs
+        kflops = {"fwd": 4.0, "dq": 6.0, "dkv": 8.0}
+        dom = max(("fwd", "dq", "dkv"), key=lambda n: kt[n])
+        ach = kflops[dom] * w["D"] * pairs / (kt[dom] * 1e-3) / 1e12
+        rows = w["B"] * w["H"] * w["S"]
+        delta_bytes = 2 * rows * w["D"] * 2 + rows * 4
+        roofline = {"kernel": f"{dom}_sm100_kernel", "bound": "tensor", "achieved": ach, "peak": peaks["tflops"],
+                    "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                    "peak_source": f"bf16_tflops (burst) of {peaks['source']} peaks",
+                    "ms_per_launch": kt[dom]}
+        per_kernel = {n: {"ms": kt[n], "tflops": kflops[n] * w["D"] * pairs / (kt[n] * 1e-3) / 1e12,
+                          "frac_of_peak": kflops[n] * w["D"] * pairs / (kt[n] * 1e-3) / 1e12 / peaks["tflops"]}
+                      for n in ("fwd", "dq", "dkv")}
+        per_kernel["delta"] = {"ms": kt["delta"], "gbs": delta_bytes / (kt["delta"] * 1e-3) / 1e9,
+                               "frac_of_hbm_peak": delta_bytes / (kt["delta"] * 1e-3) / 1e9 / peaks["hbm"]}
+        cpu_v, cores, sample, _ = cpu_reference_sample(w, budget_s=12.0) if world == 1 else (None, None, None, None)
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["desc"], "global_batch": w["B"] * world, "sharding": "batch x head, no collective",
+                       "l2": "inputs (q,k,v,do) and outputs exceed the 126 MB L2; no flush needed"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": io_bytes,
+                    "d2h_bytes_per_step": io_bytes, "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms},
+            "gpu_launches": 4 * args.steps,
+            "roofline": roofline,
+            "fwd": {"ms": fwd_ms, "tflops": flops_fwd / (fwd_ms * 1e-3) / 1e12,
+                    "frac_of_peak": flops_fwd / (fwd_ms * 1e-3) / 1e12 / peaks["tflops_sustained"]},
+            "bwd": {"ms": bwd_ms, "tflops": flops_bwd / (bwd_ms * 1e-3) / 1e12,
+                    "frac_of_peak": flops_bwd / (bwd_ms * 1e-3) / 1e12 / peaks["tflops_sustained"]},
+            "kernels": per_kernel,
+        }
+        if cpu_v is not None:
+            line["cpu_baseline"] = {"value": cpu_v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": sample}
+        if checks is not None:
+            line["verification_gather"] = checks
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

@@ -162,18 +162,21 @@ class Problem:
             doc_key = (self.doc_ids.data_ptr(), self.doc_ids._version)
         key = (self.device.index, p.mask_kind, p.window, p.stride, p.batch, p.seq_q, p.seq_k, doc_key)
         cache = Problem._map_cache
-        ws = cache.get(key) if doc_key is None else None  # doc id buffers can be recycled: always rebuild
+        hit = cache.get(key)
+        ws = None if hit is None else hit[0]
         fresh = ws is None
         if fresh:
             ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        else:
+            cache.move_to_end(key)
         p.workspace, p.workspace_bytes = ws.data_ptr(), nbytes
         self.workspace = ws
         if fresh:
             check(lib.flexattn_build_mask_map(_stream_ptr(self.device), ctypes.byref(p)), "flexattn_build_mask_map")
-            if doc_key is None:
-                cache[key] = ws
-                while len(cache) > Problem._MAP_CACHE_ENTRIES:
-                    cache.popitem(last=False)
+            # the entry keeps the doc-id tensor alive, so its (pointer, version) key cannot be recycled
+            cache[key] = (ws, self.doc_ids)
+            while len(cache) > Problem._MAP_CACHE_ENTRIES:
+                cache.popitem(last=False)
 
     def read_map(self, which: int, b: int, index: int):
         out = (ctypes.c_int32 * 4)()

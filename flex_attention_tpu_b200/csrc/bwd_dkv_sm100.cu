@@ -1,0 +1,341 @@
+// dK / dV backward on the 5th-generation tensor cores (sm_100a).
+//
+// Replaces the reference's Pallas dK/dV kernel (flex_attention_dkv_kernel.py:177-280 and its mask-aware
+// twin flash_attention_dkv_bwd.py:183-308).  One CTA owns one 128-row kv tile of one (batch, head): K and
+// V stay in shared memory, Q/dO tiles (and their row statistics) stream through a two-stage ring, and
+// per q tile the TRANSPOSED score tile is formed so that the probabilities land in tensor memory in
+// the layout the next MMA wants as its A operand:
+//
+//   S^T  = K Q^T, dP^T = V dO^T      tcgen05.mma, f32 accumulators (128 + 128 TMEM columns)
+//   P^T, dS^T                        in registers; thread t = key row t, columns = query positions, whose
+//                                    statistics (m log2e + log2 l, delta) are read from shared memory;
+//                                    written back as packed bf16 over S^T / dP^T
+//   dV += P^T dO ; dK += dS^T Q      tcgen05.mma, A from tensor memory, B = the dO / Q tile read MN-major
+//
+// dK, dV (D columns each) stay in tensor memory across q tiles: 512 columns in total, one CTA per SM.
+#include "sm100.cuh"
+
+namespace flexattn {
+namespace {
+
+constexpr int kThreads = 160;
+
+struct DkvSmem {
+  uint64_t bar_kv, bar_q[2], bar_sdp, bar_pds, bar_acc;
+  uint32_t tmem_base;
+  float lse2[2][kTile];
+  float delta[2][kTile];
+  int32_t doc[2][kTile];
+};
+
+template <int D, int SK, int MK>
+__global__ void __launch_bounds__(kThreads, 1)
+    dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                     const DevParams P, int* abort_flag) {
+  constexpr int kPanels = D / 64;
+  constexpr uint32_t kTileBytes = kPanels * ptx::kPanelBytes;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + kTileBytes;
+  uint8_t* sQ = smem + 2 * kTileBytes;   // two stages
+  uint8_t* sDO = smem + 4 * kTileBytes;  // two stages
+  DkvSmem* sh = reinterpret_cast<DkvSmem*>(smem + 6 * kTileBytes);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kt = blockIdx.x;  // early kv tiles see the most query tiles under a causal mask: run them first
+  const int bh = blockIdx.y, b = bh / P.heads, h = bh % P.heads;
+  const int4 cm = P.col_map[(size_t)(P.map_rows > 1 ? b : 0) * P.n_kt + kt];
+  const int n_tiles = cm.y - cm.x;
+
+  if (*reinterpret_cast<volatile int*>(abort_flag) != 0) return;
+
+  if (tid == 0) {
+    ptx::mbar_init(&sh->bar_kv, 1);
+    ptx::mbar_init(&sh->bar_q[0], 1);
+    ptx::mbar_init(&sh->bar_q[1], 1);
+    ptx::mbar_init(&sh->bar_sdp, 1);
+    ptx::mbar_init(&sh->bar_pds, 128);
+    ptx::mbar_init(&sh->bar_acc, 1);
+    ptx::fence_barrier_init();
+  }
+  if (warp == 4) {
+    ptx::tmem_alloc(&sh->tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = sh->tmem_base;
+
+  if (warp == 4) {
+    if (lane == 0 && n_tiles > 0) {
+      bool ok = true;
+      int fail_at = 1;
+      ptx::prefetch_tensormap(&tm_q);
+      ptx::prefetch_tensormap(&tm_do);
+      ptx::prefetch_tensormap(&tm_k);
+      ptx::prefetch_tensormap(&tm_v);
+      ptx::mbar_arrive_expect_tx(&sh->bar_kv, 2 * kTileBytes);
+      ptx::mbar_arrive_expect_tx(&sh->bar_q[0], 2 * kTileBytes);
+#pragma unroll
+      for (int p = 0; p < kPanels; ++p) {
+        ptx::tma_load_3d(sK + p * ptx::kPanelBytes, &tm_k, &sh->bar_kv, p * 64, kt * kTile, bh);
+        ptx::tma_load_3d(sV + p * ptx::kPanelBytes, &tm_v, &sh->bar_kv, p * 64, kt * kTile, bh);
+        ptx::tma_load_3d(sQ + p * ptx::kPanelBytes, &tm_q, &sh->bar_q[0], p * 64, cm.x * kTile, bh);
+        ptx::tma_load_3d(sDO + p * ptx::kPanelBytes, &tm_do, &sh->bar_q[0], p * 64, cm.x * kTile, bh);
+      }
+      constexpr uint32_t idesc_s = ptx::make_idesc(128, 128, false);
+      constexpr uint32_t idesc_acc = ptx::make_idesc(128, D, true);
+      const uint32_t aK = ptx::smem_u32(sK), aV = ptx::smem_u32(sV);
+      ok = ptx::mbar_wait(&sh->bar_kv, 0);
+      for (int n = 0; n < n_tiles && ok; ++n) {
+        const int st = n & 1;
+        const uint32_t aQ = ptx::smem_u32(sQ + st * kTileBytes), aDO = ptx::smem_u32(sDO + st * kTileBytes);
+        if (n > 0) {
+          // accumulation MMAs of the previous tile done: S^T/dP^T columns and the other Q/dO stage are free
+          ok = ptx::mbar_wait(&sh->bar_acc, (n - 1) & 1);
+          if (!ok) { fail_at = 2; break; }
+        }
+        if (n + 1 < n_tiles) {
+          uint8_t* nQ = sQ + (st ^ 1) * kTileBytes;
+          uint8_t* nDO = sDO + (st ^ 1) * kTileBytes;
+          ptx::mbar_arrive_expect_tx(&sh->bar_q[st ^ 1], 2 * kTileBytes);
+#pragma unroll
+          for (int p = 0; p < kPanels; ++p) {
+            ptx::tma_load_3d(nQ + p * ptx::kPanelBytes, &tm_q, &sh->bar_q[st ^ 1], p * 64, (cm.x + n + 1) * kTile, bh);
+            ptx::tma_load_3d(nDO + p * ptx::kPanelBytes, &tm_do, &sh->bar_q[st ^ 1], p * 64, (cm.x + n + 1) * kTile, bh);
+          }
+        }
+        ok = ptx::mbar_wait(&sh->bar_q[st], (n >> 1) & 1);
+        if (!ok) { fail_at = 3; break; }
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          ptx::mma_ss(tmem + kColS, ptx::desc_kmajor(aK, kk), ptx::desc_kmajor(aQ, kk), idesc_s, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          ptx::mma_ss(tmem + kColDP, ptx::desc_kmajor(aV, kk), ptx::desc_kmajor(aDO, kk), idesc_s, kk > 0);
+        ptx::mma_commit(&sh->bar_sdp);
+        ok = ptx::mbar_wait(&sh->bar_pds, n & 1);
+        if (!ok) { fail_at = 4; break; }
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          ptx::mma_ts(tmem + kColDV, tmem + kColS + kk * 8, ptx::desc_mnmajor(aDO, kk), idesc_acc, (n > 0) || (kk > 0));
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          ptx::mma_ts(tmem + kColDK, tmem + kColDP + kk * 8, ptx::desc_mnmajor(aQ, kk), idesc_acc, (n > 0) || (kk > 0));
+        ptx::mma_commit(&sh->bar_acc);
+      }
+      if (!ok) give_up(abort_flag, P.status, 3, fail_at);
+    }
+  } else {
+    const int row = tid;
+    const int j = kt * kTile + row;  // global key position
+    const bool row_ok = j < P.seq_k;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    const float c2 = P.sm_scale * kLog2e;
+    const float slope2 = (SK == FLEXATTN_SCORE_ALIBI) ? P.alibi_slopes[h] * kLog2e : 0.f;
+    const float capl2 = P.cap * kLog2e;
+    const float csc = (SK == FLEXATTN_SCORE_SOFTCAP) ? P.sm_scale / P.cap : 0.f;
+    const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
+    const int dj = (MK == FLEXATTN_MASK_DOCUMENT && row_ok) ? doc[j] : -2;
+    const size_t stat_base = (size_t)bh * P.seq_q;
+    bool ok = true;
+    int fail_at = 0;
+
+    for (int n = 0; n < n_tiles; ++n) {
+      const int st = n & 1;
+      const int qt = cm.x + n, i0 = qt * kTile;
+      const bool partial = !(qt >= cm.z && qt < cm.w);
+      {
+        // statistics of query row i0 + row for this tile (thread t stages row t, everyone reads all 128)
+        const int i = i0 + row;
+        float lse2 = 0.f, dl = 0.f;
+        if (i < P.seq_q) {
+          const float l = P.l[stat_base + i];
+          lse2 = l > 0.f ? fmaf(P.m[stat_base + i], kLog2e, log2f(l)) : 1.0e30f;
+          dl = P.delta[stat_base + i];
+        }
+        sh->lse2[st][row] = lse2;
+        sh->delta[st][row] = dl;
+        if (MK == FLEXATTN_MASK_DOCUMENT) sh->doc[st][row] = (i < P.seq_q) ? doc[i] : -1;
+        ptx::named_bar_sync(1, 128);
+      }
+      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_sdp, n & 1));
+      if (!ok) { fail_at = 10; break; }
+      ptx::tc_fence_after();
+      const float abase = slope2 * (float)(j - i0);  // ALiBi bias = slope * (j - i), i = i0 + column
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sr[2][32], pr[2][32];
+        ptx::tmem_ld32(lane_base + kColS + half * 64, sr[0]);
+        ptx::tmem_ld32(lane_base + kColS + half * 64 + 32, sr[1]);
+        ptx::tmem_ld32(lane_base + kColDP + half * 64, pr[0]);
+        ptx::tmem_ld32(lane_base + kColDP + half * 64 + 32, pr[1]);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld_acquire(sr[0]);
+        ptx::tmem_ld_acquire(sr[1]);
+        ptx::tmem_ld_acquire(pr[0]);
+        ptx::tmem_ld_acquire(pr[1]);
+        uint32_t pk_p[32], pk_ds[32];
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          float p2[2], ds2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int cc = half * 64 + c + u;  // column inside the tile = query row offset
+            const float s = __uint_as_float(sr[(c + u) >> 5][(c + u) & 31]);
+            const float dp = __uint_as_float(pr[(c + u) >> 5][(c + u) & 31]);
+            float x2, dsig = 1.f;
+            if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
+              x2 = fmaf(s, c2, fmaf(-slope2, (float)cc, abase));
+            } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+              const float th = ptx::tanh_approx(s * csc);
+              x2 = capl2 * th;
+              dsig = fmaf(-th, th, 1.f);
+            } else {
+              x2 = s * c2;
+            }
+            float p = ptx::ex2(x2 - sh->lse2[st][cc]);
+            if (partial) {
+              const int i = i0 + cc;
+              const int di = (MK == FLEXATTN_MASK_DOCUMENT) ? sh->doc[st][cc] : 0;
+              const bool keep = (i < P.seq_q) && mask_keep<MK>(i, j, P.window, P.stride, di, dj);
+              p = keep ? p : 0.f;
+            }
+            float d = p * (dp - sh->delta[st][cc]);
+            if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) d *= dsig;
+            p2[u] = p;
+            ds2[u] = d;
+          }
+          pk_p[c >> 1] = ptx::pack_bf16(p2[0], p2[1]);
+          pk_ds[c >> 1] = ptx::pack_bf16(ds2[0], ds2[1]);
+        }
+        ptx::tmem_st32(lane_base + kColS + half * 32, pk_p);
+        ptx::tmem_st32(lane_base + kColDP + half * 32, pk_ds);
+      }
+      ptx::tmem_wait_st();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(&sh->bar_pds);
+    }
+
+    if (ok && n_tiles > 0) {
+      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_acc, (n_tiles - 1) & 1));
+      if (!ok) fail_at = 12;
+    }
+    if (ok) {
+      if (n_tiles > 0) ptx::tc_fence_after();
+      const size_t grow = (size_t)bh * P.seq_k + j;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(which ? P.dv : P.dk) + grow * D;
+        const float sc = which ? 1.f : P.sm_scale;
+        const uint32_t col = which ? kColDV : kColDK;
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t r[32];
+          if (n_tiles > 0) {
+            ptx::tmem_ld32(lane_base + col + c0, r);
+            ptx::tmem_wait_ld();
+            ptx::tmem_ld_acquire(r);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) r[c] = 0u;
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+              uint4 v4;
+              v4.x = ptx::pack_bf16(__uint_as_float(r[c]) * sc, __uint_as_float(r[c + 1]) * sc);
+              v4.y = ptx::pack_bf16(__uint_as_float(r[c + 2]) * sc, __uint_as_float(r[c + 3]) * sc);
+              v4.z = ptx::pack_bf16(__uint_as_float(r[c + 4]) * sc, __uint_as_float(r[c + 5]) * sc);
+              v4.w = ptx::pack_bf16(__uint_as_float(r[c + 6]) * sc, __uint_as_float(r[c + 7]) * sc);
+              *reinterpret_cast<uint4*>(out + c0 + c) = v4;
+            }
+          }
+        }
+      }
+    } else if (lane == 0) {
+      give_up(abort_flag, P.status, 3, fail_at);
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+template <int D, int SK, int MK>
+int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const CUtensorMap& tdo,
+               const CUtensorMap& tk, const CUtensorMap& tv, int* abort_flag) {
+  constexpr size_t smem = 6 * (D / 64) * ptx::kPanelBytes + sizeof(DkvSmem) + 1024;
+  // 512 TMEM columns per CTA: never let two CTAs share an SM (the second would spin in tcgen05.alloc)
+  constexpr size_t smem_req = smem > 120 * 1024 ? smem : 120 * 1024;
+  auto kern = dkv_sm100_kernel<D, SK, MK>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_req) != cudaSuccess)
+      return FLEXATTN_ERR_CUDA;
+    attr_set = true;
+  }
+  dim3 grid(d.n_kt, d.batch * d.heads);
+  kern<<<grid, kThreads, smem_req, st>>>(tq, tdo, tk, tv, d, abort_flag);
+  return cudaGetLastError() == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;
+}
+
+template <int D, int SK>
+int launch_mask(cudaStream_t st, const DevParams& d, int mask, const CUtensorMap& tq, const CUtensorMap& tdo,
+                const CUtensorMap& tk, const CUtensorMap& tv, int* af) {
+  switch (mask) {
+    case FLEXATTN_MASK_NONE: return launch_one<D, SK, FLEXATTN_MASK_NONE>(st, d, tq, tdo, tk, tv, af);
+    case FLEXATTN_MASK_CAUSAL: return launch_one<D, SK, FLEXATTN_MASK_CAUSAL>(st, d, tq, tdo, tk, tv, af);
+    case FLEXATTN_MASK_SLIDING_WINDOW: return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW>(st, d, tq, tdo, tk, tv, af);
+    case FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL:
+      return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL>(st, d, tq, tdo, tk, tv, af);
+    case FLEXATTN_MASK_DOCUMENT: return launch_one<D, SK, FLEXATTN_MASK_DOCUMENT>(st, d, tq, tdo, tk, tv, af);
+    case FLEXATTN_MASK_S2: return launch_one<D, SK, FLEXATTN_MASK_S2>(st, d, tq, tdo, tk, tv, af);
+    default: return FLEXATTN_ERR_UNSUPPORTED_MOD;
+  }
+}
+
+template <int D>
+int launch_score(cudaStream_t st, const DevParams& d, int score, int mask, const CUtensorMap& tq,
+                 const CUtensorMap& tdo, const CUtensorMap& tk, const CUtensorMap& tv, int* af) {
+  switch (score) {
+    case FLEXATTN_SCORE_NONE: return launch_mask<D, FLEXATTN_SCORE_NONE>(st, d, mask, tq, tdo, tk, tv, af);
+    case FLEXATTN_SCORE_ALIBI: return launch_mask<D, FLEXATTN_SCORE_ALIBI>(st, d, mask, tq, tdo, tk, tv, af);
+    case FLEXATTN_SCORE_SOFTCAP: return launch_mask<D, FLEXATTN_SCORE_SOFTCAP>(st, d, mask, tq, tdo, tk, tv, af);
+    default: return FLEXATTN_ERR_UNSUPPORTED_MOD;
+  }
+}
+
+}  // namespace
+
+int launch_sm100_dkv(cudaStream_t st, const DevParams& d, int score, int mask) {
+  int* af = abort_flag_ptr();
+  if (af == nullptr) return FLEXATTN_ERR_CUDA;
+  CUtensorMap tq, tdo, tk, tv;
+  const int slices = d.batch * d.heads;
+  int e = make_tile_map(&tq, d.q, slices, d.seq_q, d.head_dim);
+  if (e) return e;
+  e = make_tile_map(&tdo, d.d_o, slices, d.seq_q, d.head_dim);
+  if (e) return e;
+  e = make_tile_map(&tk, d.k, slices, d.seq_k, d.head_dim);
+  if (e) return e;
+  e = make_tile_map(&tv, d.v, slices, d.seq_k, d.head_dim);
+  if (e) return e;
+  if (d.head_dim == 128) return launch_score<128>(st, d, score, mask, tq, tdo, tk, tv, af);
+  if (d.head_dim == 64) return launch_score<64>(st, d, score, mask, tq, tdo, tk, tv, af);
+  return FLEXATTN_ERR_UNSUPPORTED_HEAD_DIM;
+}
+
+}  // namespace flexattn

@@ -118,5 +118,5 @@ def test_tensor_core_matches_simt_on_long_rows():
     a = run_hot_path(fa, q, k, v, do, sm_scale=sm, mask_kind="causal", backend="tcgen05")
     b = run_hot_path(fa, q, k, v, do, sm_scale=sm, mask_kind="causal", backend="simt")
     for n in ("o", "dq", "dk", "dv"):
-        e = errors(a[n], b[n].float().cpu().numpy())
-        assert e["max_abs"] <= TOL[torch.bfloat16]["abs"] and e["max_rel"] <= TOL[torch.bfloat16]["rel"], (n, e)
+        e = errors(a[n], b[n].float().cpu().numpy(), 2 * TOL[torch.bfloat16]["round"])   # both sides stored in bf16
+        assert e["max_abs_excess"] <= TOL[torch.bfloat16]["abs"] and e["max_rel"] <= TOL[torch.bfloat16]["rel"], (n, e)
