@@ -44,7 +44,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel on the c2 workload, from
 # the ncu capture summarised under profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES = {"c2": None}
+NCU_TRAFFIC_BYTES = {"c2": {"fwd": 252.7e6, "dq": 324.8e6, "dkv": 377.1e6}}
 
 
 def measured_peaks():
@@ -73,22 +73,26 @@ def total_pairs(w, doc_ids=None):
 
 # ------------------------------------------------------------------------------------------ clocks
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi sampling in a child process.  Started well before the timed region (its start-up talks
+    to the driver and would disturb the first launches otherwise); samples are kept only if their
+    timestamp falls inside the window given to stop()."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
-        self.proc, self.index = None, index
+    def __init__(self, index, period_ms=20):
+        self.proc, self.index, self.period_ms = None, index, period_ms
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
-    def stop(self):
+    def stop(self, t_begin, t_end):
+        import datetime
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
         self.proc.terminate()
@@ -97,24 +101,30 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        rows = []
         for line in out.strip().splitlines():
             parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 7:
+            if len(parts) < 8:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(parts[1]), float(parts[2]), float(parts[3]),
+                             [n for n, v in zip(names, parts[4:8]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
+        inside = [r for r in rows if t_begin <= r[0] <= t_end]
+        note = "samples inside the timed region"
+        if not inside and rows:   # region shorter than the sampling period: take the nearest sample
+            mid = 0.5 * (t_begin + t_end)
+            inside = [min(rows, key=lambda r: abs(r[0] - mid))]
+            note = "timed region shorter than the sampling period: nearest sample"
+        if not inside:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
-        return dict(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons),
-                    samples=len(sm))
+        reasons = sorted({x for r in inside for x in r[4]})
+        return dict(sm_mhz=float(np.median([r[1] for r in inside])), sm_max_mhz=float(max(r[2] for r in inside)),
+                    power_w=float(np.median([r[3] for r in inside])), reasons=reasons, samples=len(inside),
+                    note=note)
 
 
 # ------------------------------------------------------------------------------------------ inputs
@@ -253,7 +263,7 @@ def run_reference_arm(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    per_step_budget = max(2.0, min(15.0, 120.0 / max(1, args.steps + args.warmup)))
+    per_step_budget = min(15.0, 150.0 / max(1, args.steps + args.warmup))
     vals, sample, cores = [], "", 1
     for it in range(args.warmup + args.steps):
         v, cores, sample, _ = cpu_reference_sample(w, budget_s=per_step_budget)
@@ -304,11 +314,15 @@ def run_ours(args, w):
     flops_bwd = 10.0 * w["D"] * pairs
 
     # ---- device-resident timing: W warm-up steps, K timed steps, CUDA events, max over ranks
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    hp.step(q, k, v, do)
+    torch.cuda.synchronize()
+    time.sleep(0.5)                      # let the sampler finish starting up before anything is timed
     for _ in range(args.warmup):
         hp.step(q, k, v, do)
-    sampler = ClockSampler(local_rank)
     barrier()
-    sampler.start()
+    t_begin = time.time()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ef = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     e0.record()
@@ -319,7 +333,8 @@ def run_ours(args, w):
         ef[s][1].record()
     e1.record()
     barrier()
-    clocks = sampler.stop()
+    t_end = time.time()
+    clocks = sampler.stop(t_begin, t_end)
     total_ms = max_over_ranks(e0.elapsed_time(e1))
     ms_step = total_ms / args.steps
     # split of the step into fwd / bwd (this rank)
@@ -344,7 +359,7 @@ def run_ours(args, w):
         for h_, r in zip(host_out, res):
             h_.copy_(r, non_blocking=True)
 
-    e2e_steps = max(1, min(args.steps, 5))
+    e2e_steps = 0 if args.skip_e2e else max(1, min(args.steps, 5))
     e2e_step()
     barrier()
     t0 = time.perf_counter()
@@ -354,9 +369,9 @@ def run_ours(args, w):
         e2e_step()
     g1.record()
     barrier()
-    e2e_ms = max_over_ranks(g0.elapsed_time(g1)) / e2e_steps
-    e2e_wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    e2e_value = world * (flops_fwd + flops_bwd) / (e2e_ms * 1e-3) / 1e12
+    e2e_ms = max_over_ranks(g0.elapsed_time(g1)) / max(e2e_steps, 1)
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3 / max(e2e_steps, 1)
+    e2e_value = world * (flops_fwd + flops_bwd) / (e2e_ms * 1e-3) / 1e12 if e2e_steps else None
     io_bytes = sum(t.numel() * t.element_size() for t in host_in)
 
     # ---- verification gather over NCCL (outside every timed region): per-rank checksums of the outputs
@@ -377,7 +392,7 @@ def run_ours(args, w):
         rows = w["B"] * w["H"] * w["S"]
         delta_bytes = 2 * rows * w["D"] * 2 + rows * 4
         roofline = {"kernel": f"{dom}_sm100_kernel", "bound": "tensor", "achieved": ach, "peak": peaks["tflops"],
-                    "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                    "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "traffic": (NCU_TRAFFIC_BYTES.get(args.workload) or {}).get(dom),
                     "peak_source": f"bf16_tflops (burst) of {peaks['source']} peaks",
                     "ms_per_launch": kt[dom]}
         per_kernel = {n: {"ms": kt[n], "tflops": kflops[n] * w["D"] * pairs / (kt[n] * 1e-3) / 1e12,
@@ -385,7 +400,8 @@ def run_ours(args, w):
                       for n in ("fwd", "dq", "dkv")}
         per_kernel["delta"] = {"ms": kt["delta"], "gbs": delta_bytes / (kt["delta"] * 1e-3) / 1e9,
                                "frac_of_hbm_peak": delta_bytes / (kt["delta"] * 1e-3) / 1e9 / peaks["hbm"]}
-        cpu_v, cores, sample, _ = cpu_reference_sample(w, budget_s=12.0) if world == 1 else (None, None, None, None)
+        cpu_v, cores, sample, _ = (cpu_reference_sample(w, budget_s=12.0)
+                                   if world == 1 and not args.skip_cpu_baseline else (None, None, None, None))
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -417,10 +433,12 @@ def run_ours(args, w):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the cpu_baseline leg (profiling runs)")
+    ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]

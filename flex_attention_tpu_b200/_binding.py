@@ -137,12 +137,7 @@ class Problem:
             self._keep.append(doc_ids)
         self.doc_ids = doc_ids if mask_kind == MASK_DOCUMENT else None
         if score_kind == SCORE_ALIBI:
-            slopes = torch.as_tensor(alibi_slopes, dtype=torch.float32).flatten()
-            if slopes.numel() == 1:
-                slopes = slopes.expand(H)
-            if slopes.numel() != H:
-                raise ValueError(f"need one ALiBi slope per head ({H}), got {slopes.numel()}")
-            slopes = slopes.to(self.device).contiguous()
+            slopes = self._device_slopes(alibi_slopes, H)
             p.alibi_slopes = slopes.data_ptr()
             self._keep.append(slopes)
         if status is not None:
@@ -150,6 +145,33 @@ class Problem:
             self._keep.append(status)
         self.p = p
         self._bind_workspace()
+
+    _slope_cache: "OrderedDict[tuple, torch.Tensor]" = OrderedDict()
+
+    def _device_slopes(self, alibi_slopes, H):
+        """[H] float32 slopes on the device.  Host values are uploaded once and cached: a pageable
+        host-to-device copy waits for the stream, which would serialise every call behind the last."""
+        if isinstance(alibi_slopes, torch.Tensor) and alibi_slopes.is_cuda:
+            slopes = alibi_slopes.to(torch.float32).flatten()
+            if slopes.numel() == 1:
+                slopes = slopes.expand(H)
+            if slopes.numel() != H:
+                raise ValueError(f"need one ALiBi slope per head ({H}), got {slopes.numel()}")
+            return slopes.contiguous()
+        vals = tuple(float(x) for x in torch.as_tensor(alibi_slopes, dtype=torch.float32).flatten().tolist())
+        if len(vals) == 1:
+            vals = vals * H
+        if len(vals) != H:
+            raise ValueError(f"need one ALiBi slope per head ({H}), got {len(vals)}")
+        key = (self.device.index, vals)
+        cache = Problem._slope_cache
+        t = cache.get(key)
+        if t is None:
+            t = torch.tensor(vals, dtype=torch.float32).to(self.device)
+            cache[key] = t
+            while len(cache) > 16:
+                cache.popitem(last=False)
+        return t
 
     # ------------------------------------------------------------------ mask map
     def _bind_workspace(self):
