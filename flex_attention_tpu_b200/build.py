@@ -1,4 +1,4 @@
-"""Builds libflexattn.so (sm_100a only) in-tree with nvcc.  Usage: python -m flex_attention_tpu_b200.build [-v]"""
+"""Builds libflexattn.so (sm_100a only) in-tree with nvcc.  Usage: python flex_attention_tpu_b200/build.py [-v]"""
 from __future__ import annotations
 
 import concurrent.futures
