@@ -50,7 +50,7 @@ class FlexAttnError(RuntimeError):
 def _load():
     if not os.path.exists(_LIB_PATH):
         raise ImportError(
-            f"{_LIB_PATH} is missing: build it with `python -m flex_attention_tpu_b200.build` "
+            f"{_LIB_PATH} is missing: build it with `python flex_attention_tpu_b200/build.py` "
             "(there is no fallback implementation)")
     lib = ctypes.CDLL(_LIB_PATH)
     P = ctypes.POINTER(FlexAttnParams)
@@ -64,6 +64,9 @@ def _load():
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [ctypes.c_void_p, P]
+    lib.flexattn_fwd_noalloc.restype = ctypes.c_int
+    lib.flexattn_fwd_noalloc.argtypes = [ctypes.c_void_p, P]
+    lib.flexattn_noalloc_scratch_bytes.restype = ctypes.c_size_t
     lib.flexattn_read_mask_map.restype = ctypes.c_int
     lib.flexattn_read_mask_map.argtypes = [ctypes.c_void_p, P, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                            ctypes.POINTER(ctypes.c_int32)]

@@ -106,6 +106,8 @@ const char* flexattn_status_string(int status) {
     case FLEXATTN_ERR_CUDA: return "CUDA error at launch";
     case FLEXATTN_ERR_TIMEOUT: return "device-side wait timed out";
     case FLEXATTN_ERR_UNSUPPORTED_BACKEND: return "backend cannot serve this dtype / head_dim";
+    case FLEXATTN_ERR_NOALLOC_LIMIT:
+      return "mask map larger than the fixed scratch array of the no-allocation entry point (1 MiB)";
     default: return "unknown status";
   }
 }

@@ -44,7 +44,8 @@ typedef enum FlexAttnStatus {
   FLEXATTN_ERR_UNSUPPORTED_MOD = 7,
   FLEXATTN_ERR_CUDA = 8,
   FLEXATTN_ERR_TIMEOUT = 9,
-  FLEXATTN_ERR_UNSUPPORTED_BACKEND = 10
+  FLEXATTN_ERR_UNSUPPORTED_BACKEND = 10,
+  FLEXATTN_ERR_NOALLOC_LIMIT = 11
 } FlexAttnStatus;
 
 typedef enum FlexAttnDType { FLEXATTN_BF16 = 0, FLEXATTN_F32 = 1 } FlexAttnDType;
@@ -143,6 +144,29 @@ int flexattn_bwd_dq(void* stream, const FlexAttnParams* p);
 /* dK and dV.  Replaces `flash_attention_bwd_dkv` (flex_attention_dkv_kernel.py:23-174 and its
  * mask-aware twin flash_attention_dkv_bwd.py:27-180).  Reads q,k,v,do,l,m,delta. */
 int flexattn_bwd_dkv(void* stream, const FlexAttnParams* p);
+
+/* Forward without any caller-provided scratch memory.  It has no counterpart in the reference.
+ *
+ * For hosts that cannot allocate device memory and were handed only operands and results: code running
+ * under a memory planner that assigned every buffer before launch, or inside a process whose allocator
+ * owns the whole device.  Same inputs and outputs as flexattn_fwd (q, k, v -> o, l, m; doc_ids /
+ * alibi_slopes as the mask / score kinds require); `workspace` and `workspace_bytes` are ignored.  The
+ * mask map is built, on `stream`, into a fixed array of flexattn_noalloc_scratch_bytes() = 1 MiB that is
+ * part of the library's device image (each GPU that loads the library carries it until the process
+ * exits), then the forward kernel runs from it.  Nothing is allocated or freed, by the CUDA runtime or
+ * by any library, on any call.
+ *
+ *  - A problem whose mask map needs more than that (flexattn_workspace_bytes(p) > 1 MiB) is refused with
+ *    FLEXATTN_ERR_NOALLOC_LIMIT; use flexattn_fwd with your own workspace instead.
+ *  - The first call on each device resolves the array's device address (cudaGetSymbolAddress, with that
+ *    device current).  Make that first call outside any stream capture.
+ *  - All calls on a device share the one array, which always holds the map of the most recent call.  Calls
+ *    whose GPU work can overlap (different streams, or threads that do not order their launches) race on
+ *    it: serialise them, e.g. by using a single stream. */
+int flexattn_fwd_noalloc(void* stream, const FlexAttnParams* p);
+
+/* Size in bytes of the fixed scratch array behind flexattn_fwd_noalloc.  No counterpart in the reference. */
+size_t flexattn_noalloc_scratch_bytes(void);
 
 /* Decodes the mask map in `workspace` for tests and tools: copies entry `index` of the row map
  * (which = 0: per q tile) or column map (which = 1: per kv tile) of batch row `b` into out[4] =

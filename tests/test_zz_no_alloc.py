@@ -1,0 +1,95 @@
+"""flexattn_fwd_noalloc: the forward for hosts that cannot allocate device memory (a plugin under a memory
+planner that fixed every buffer up front, a process whose allocator owns the whole device).  Its mask map
+lives in a fixed array inside the library instead of a caller workspace.
+
+Called here straight through the C ABI, twice in a row with different problems (the array is shared and keeps
+the previous call's map, so the second call proves it is rewritten), and compared with flexattn_fwd run on a
+caller-owned workspace.  Both paths launch the same kernel on the same inputs, so the outputs must agree
+exactly; the assertion still uses the suite's bf16 tolerance as its bound.  This file sorts last on purpose:
+a run that stops at the first failure has then already executed every other test."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL, errors, make_qkvdo
+
+pytestmark = pytest.mark.gpu
+
+
+def _params(B, mod, q, k, v, o, l, m, *, mask_kind, score_kind=0, window=0, doc=None, slopes=None, cap=0.0):
+    p = B.FlexAttnParams()
+    p.q, p.k, p.v, p.o, p.l, p.m = (t.data_ptr() for t in (q, k, v, o, l, m))
+    p.batch, p.heads, p.seq_q, p.head_dim = q.shape
+    p.seq_k = k.shape[2]
+    p.dtype = B.DTYPE_BF16
+    p.sm_scale = 1.0 / float(np.sqrt(q.shape[3]))
+    p.mask_kind, p.window, p.score_kind, p.softcap = mask_kind, window, score_kind, cap
+    if doc is not None:
+        p.doc_ids = doc.data_ptr()
+    if slopes is not None:
+        p.alibi_slopes = slopes.data_ptr()
+    return p
+
+
+def _run_both(B, q, k, v, **kw):
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    outs = []
+    for noalloc in (False, True):
+        o = torch.full_like(q, float("nan"))
+        l = torch.full(q.shape[:3], float("nan"), dtype=torch.float32, device="cuda")
+        m = torch.full_like(l, float("nan"))
+        p = _params(B, None, q, k, v, o, l, m, **kw)
+        if noalloc:
+            rc = B.lib.flexattn_fwd_noalloc(stream, ctypes.byref(p))      # no workspace in p at all
+            assert rc == 0, B.status_string(rc)
+        else:
+            n = B.lib.flexattn_workspace_bytes(ctypes.byref(p))
+            ws = torch.empty(n, dtype=torch.uint8, device="cuda")
+            p.workspace, p.workspace_bytes = ws.data_ptr(), n
+            assert B.lib.flexattn_build_mask_map(stream, ctypes.byref(p)) == 0
+            assert B.lib.flexattn_fwd(stream, ctypes.byref(p)) == 0
+        torch.cuda.synchronize()
+        outs.append((o, l, m))
+    return outs
+
+
+def test_noalloc_forward_matches_workspace_forward_twice_in_a_row():
+    from flex_attention_tpu_b200 import _binding as B
+    from flex_attention_tpu_b200 import workloads
+    assert B.lib.flexattn_noalloc_scratch_bytes() == 1 << 20
+    tol = TOL[torch.bfloat16]
+
+    # call 1: causal, ragged length; call 2 (same array, different map layout): per-row documents + ALiBi
+    (q, k, v, _), _ = make_qkvdo((2, 2, 700, 128), (2, 2, 700, 128), 41, torch.bfloat16)
+    first = _run_both(B, q, k, v, mask_kind=B.MASK_CAUSAL)
+    doc_np, _ = workloads.draw_documents(np.random.default_rng(5), 2, 1000, lo=50, hi=300)
+    doc = torch.from_numpy(doc_np).cuda()
+    slopes = torch.tensor([0.5, 0.25, 0.125], device="cuda")
+    (q2, k2, v2, _), _ = make_qkvdo((2, 3, 1000, 64), (2, 3, 1000, 64), 42, torch.bfloat16)
+    second = _run_both(B, q2, k2, v2, mask_kind=B.MASK_DOCUMENT, score_kind=B.SCORE_ALIBI, doc=doc, slopes=slopes)
+
+    for (ref, got) in (first, second):
+        for name, a, b in zip(("o", "l", "m"), ref, got):
+            assert torch.isfinite(b.float()).all(), name
+            e = errors(b, a.float().cpu().numpy(), tol["round"])
+            assert e["max_abs_excess"] <= tol["abs"] and e["max_rel"] <= tol["rel"], (name, e)
+            assert torch.equal(a, b), f"{name}: same kernel, same inputs, different scratch location"
+
+
+def test_noalloc_refuses_what_does_not_fit():
+    from flex_attention_tpu_b200 import _binding as B
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = B.FlexAttnParams()
+    dummy = torch.zeros(64, dtype=torch.int32, device="cuda")
+    p.q = p.k = p.v = p.o = p.l = p.m = p.doc_ids = dummy.data_ptr()   # never dereferenced: refused first
+    # 64 document rows x 2 x 512 tiles x 16 B + 64 x 512 x 8 B > 1 MiB
+    p.batch, p.heads, p.seq_q, p.seq_k, p.head_dim = 64, 1, 65536, 65536, 128
+    p.mask_kind = B.MASK_DOCUMENT
+    assert B.lib.flexattn_workspace_bytes(ctypes.byref(p)) > (1 << 20)
+    rc = B.lib.flexattn_fwd_noalloc(stream, ctypes.byref(p))
+    assert rc == 11 and "1 MiB" in B.status_string(rc)
+    assert B.lib.flexattn_fwd_noalloc(stream, None) == 1
+    p.head_dim = 48
+    assert B.lib.flexattn_fwd_noalloc(stream, ctypes.byref(p)) == 4      # ordinary validation still speaks
