@@ -90,6 +90,12 @@ class ClockSampler:
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
+            return
+        # block until the first sample arrives: nvidia-smi's start-up (driver/NVML initialisation) must be
+        # over before anything is timed
+        import select
+        ready, _, _ = select.select([self.proc.stdout], [], [], 15.0)
+        self.first = self.proc.stdout.readline() if ready else ""
 
     def stop(self, t_begin, t_end):
         import datetime
@@ -101,6 +107,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
+        out = getattr(self, "first", "") + out
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         rows = []
         for line in out.strip().splitlines():
@@ -318,7 +325,6 @@ def run_ours(args, w):
     sampler.start()
     hp.step(q, k, v, do)
     torch.cuda.synchronize()
-    time.sleep(0.5)                      # let the sampler finish starting up before anything is timed
     for _ in range(args.warmup):
         hp.step(q, k, v, do)
     barrier()

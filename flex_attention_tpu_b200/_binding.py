@@ -11,7 +11,9 @@ from collections import OrderedDict
 
 import torch
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libflexattn.so")
+# FLEXATTN_LIBRARY points at an alternative build of the same library (e.g. an instrumented one)
+_LIB_PATH = os.environ.get("FLEXATTN_LIBRARY") or os.path.join(os.path.dirname(os.path.abspath(__file__)),
+                                                               "libflexattn.so")
 
 DTYPE_BF16, DTYPE_F32 = 0, 1
 SCORE_NONE, SCORE_ALIBI, SCORE_SOFTCAP = 0, 1, 2

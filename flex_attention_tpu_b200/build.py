@@ -9,11 +9,14 @@ import sys
 
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
-OBJ = os.path.join(PKG, "build")
-LIB = os.path.join(PKG, "libflexattn.so")
+# FLEXATTN_DEFINES (e.g. "-DFLEXATTN_TRACE") builds an instrumented variant into its own directory / file
+DEFINES = os.environ.get("FLEXATTN_DEFINES", "").split()
+_TAG = ("_" + hashlib.sha256(" ".join(DEFINES).encode()).hexdigest()[:8]) if DEFINES else ""
+OBJ = os.path.join(PKG, "build" + _TAG)
+LIB = os.environ.get("FLEXATTN_OUT", os.path.join(PKG, "libflexattn.so")) if DEFINES else os.path.join(PKG, "libflexattn.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", *DEFINES]
 
 
 def _sources():

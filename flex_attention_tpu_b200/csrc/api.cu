@@ -1,11 +1,14 @@
 // The C ABI of libflexattn.so: argument validation, backend choice and dispatch.  No allocation, no
 // host synchronisation (except flexattn_read_mask_map, a test/tool helper), no global mutable state.
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
 
 namespace flexattn {
 namespace {
+
+constexpr int kPipeMinSeqK = 1024;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -50,8 +53,15 @@ bool use_tcgen05(const FlexAttnParams* p, int* err) {
   return capable;
 }
 
+#ifdef FLEXATTN_TRACE
+long long* g_trace_buffer = nullptr;
+#endif
+
 DevParams make_dev(const FlexAttnParams* p) {
   DevParams d{};
+#ifdef FLEXATTN_TRACE
+  d.trace = g_trace_buffer;
+#endif
   MapLayout L = map_layout(p->batch, p->seq_q, p->seq_k, p->mask_kind);
   char* ws = static_cast<char*>(p->workspace);
   d.q = p->q; d.k = p->k; d.v = p->v; d.o = p->o; d.d_o = p->d_o;
@@ -90,6 +100,10 @@ int prologue(const FlexAttnParams* p) {
 using namespace flexattn;
 
 extern "C" {
+
+#ifdef FLEXATTN_TRACE
+void flexattn_debug_set_trace(void* device_buffer) { g_trace_buffer = static_cast<long long*>(device_buffer); }
+#endif
 
 int flexattn_abi_version(void) { return FLEXATTN_ABI_VERSION; }
 
@@ -133,7 +147,15 @@ int flexattn_fwd(void* stream, const FlexAttnParams* p) {
   if (e) return e;
   DevParams d = make_dev(p);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (tc) return launch_sm100_fwd(st, d, p->score_kind, p->mask_kind);
+  if (tc) {
+    // Two forward kernels: the pipelined one (three score tiles in flight, one CTA per SM) wins once a row
+    // has enough kv tiles to amortise its longer prologue; FLEXATTN_FWD_VARIANT=1|2 forces one (tests).
+    int variant = 0;
+    if (const char* env = getenv("FLEXATTN_FWD_VARIANT")) variant = atoi(env);
+    if (variant != 1 && variant != 2) variant = p->seq_k >= kPipeMinSeqK ? 2 : 1;
+    return variant == 2 ? launch_sm100_fwd_pipe(st, d, p->score_kind, p->mask_kind)
+                        : launch_sm100_fwd(st, d, p->score_kind, p->mask_kind);
+  }
   return launch_simt_fwd(st, d, p->dtype, p->score_kind, p->mask_kind) == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;
 }
 

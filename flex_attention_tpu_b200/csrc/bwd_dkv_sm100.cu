@@ -15,6 +15,16 @@
 // dK, dV (D columns each) stay in tensor memory across q tiles: 512 columns in total, one CTA per SM.
 #include "sm100.cuh"
 
+#ifdef FLEXATTN_TRACE
+#define FA_TRACE(slot)                                                          \
+  do {                                                                          \
+    if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64)     \
+      P.trace[n * 16 + (slot)] = clock64();                                     \
+  } while (0)
+#else
+#define FA_TRACE(slot)
+#endif
+
 namespace flexattn {
 namespace {
 
@@ -23,10 +33,61 @@ constexpr int kThreads = 160;
 struct DkvSmem {
   uint64_t bar_kv, bar_q[2], bar_sdp, bar_pds, bar_acc;
   uint32_t tmem_base;
-  float lse2[2][kTile];
-  float delta[2][kTile];
-  int32_t doc[2][kTile];
+  alignas(16) float nlse2[2][kTile];  // -(m log2e + log2 l) of the query rows of the tile in flight
+  alignas(16) float delta[2][kTile];
+  alignas(16) int32_t doc[2][kTile];
 };
+
+// One 64-column half of a transposed tile: this thread's key row against query columns i_first .. i_first+63.
+// sr / pr: raw S^T and dP^T values; outputs packed bf16 P^T and dS^T.  Query statistics come from shared memory
+// four at a time.  The mask functor is compiled in only for partial tiles.
+template <int SK, int MK, bool kPartial>
+__device__ __forceinline__ void dkv_half_math(const uint32_t (&sr)[2][32], const uint32_t (&pr)[2][32],
+                                              uint32_t (&pk_p)[32], uint32_t (&pk_ds)[32],
+                                              const float* __restrict__ s_nlse2, const float* __restrict__ s_delta,
+                                              const int32_t* __restrict__ s_doc, int i_first, int j, int dj, int seq_q,
+                                              int window, int stride, float c2, float slope2, float abase, float capl2,
+                                              float csc) {
+#pragma unroll
+  for (int c = 0; c < 64; c += 4) {
+    const float4 nl4 = *reinterpret_cast<const float4*>(s_nlse2 + c);
+    const float4 dl4 = *reinterpret_cast<const float4*>(s_delta + c);
+    const float nl[4] = {nl4.x, nl4.y, nl4.z, nl4.w};
+    const float dl[4] = {dl4.x, dl4.y, dl4.z, dl4.w};
+    float pv[4], dv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int cc = c + u;
+      const float s = __uint_as_float(sr[cc >> 5][cc & 31]);
+      const float dp = __uint_as_float(pr[cc >> 5][cc & 31]);
+      float arg, dsig = 1.f;  // arg = log2-domain logit minus the row's log-sum-exp
+      if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
+        arg = fmaf(s, c2, fmaf(-slope2, (float)cc, abase) + nl[u]);
+      } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+        const float th = ptx::tanh_approx(s * csc);
+        arg = fmaf(capl2, th, nl[u]);
+        dsig = fmaf(-th, th, 1.f);
+      } else {
+        arg = fmaf(s, c2, nl[u]);
+      }
+      float p = ptx::ex2(arg);
+      if constexpr (kPartial) {
+        const int i = i_first + cc;
+        const int di = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[cc] : 0;
+        const bool keep = (i < seq_q) && mask_keep<MK>(i, j, window, stride, di, dj);
+        p = keep ? p : 0.f;
+      }
+      float d = p * (dp - dl[u]);
+      if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) d *= dsig;
+      pv[u] = p;
+      dv[u] = d;
+    }
+    pk_p[c >> 1] = ptx::pack_bf16_trunc(pv[0], pv[1]);
+    pk_p[(c >> 1) + 1] = ptx::pack_bf16_trunc(pv[2], pv[3]);
+    pk_ds[c >> 1] = ptx::pack_bf16_trunc(dv[0], dv[1]);
+    pk_ds[(c >> 1) + 1] = ptx::pack_bf16_trunc(dv[2], dv[3]);
+  }
+}
 
 template <int D, int SK, int MK>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -91,11 +152,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       constexpr uint32_t idesc_s = ptx::make_idesc(128, 128, false);
       constexpr uint32_t idesc_acc = ptx::make_idesc(128, D, true);
-      const uint32_t aK = ptx::smem_u32(sK), aV = ptx::smem_u32(sV);
+      const ptx::DescBase bK = ptx::base_kmajor(ptx::smem_u32(sK)), bV = ptx::base_kmajor(ptx::smem_u32(sV));
       ok = ptx::mbar_wait(&sh->bar_kv, 0);
       for (int n = 0; n < n_tiles && ok; ++n) {
         const int st = n & 1;
-        const uint32_t aQ = ptx::smem_u32(sQ + st * kTileBytes), aDO = ptx::smem_u32(sDO + st * kTileBytes);
+        const ptx::DescBase bQ = ptx::base_kmajor(ptx::smem_u32(sQ + st * kTileBytes)),
+                            bDO = ptx::base_kmajor(ptx::smem_u32(sDO + st * kTileBytes)),
+                            bQt = ptx::base_mnmajor(ptx::smem_u32(sQ + st * kTileBytes)),
+                            bDOt = ptx::base_mnmajor(ptx::smem_u32(sDO + st * kTileBytes));
         if (n > 0) {
           // accumulation MMAs of the previous tile done: S^T/dP^T columns and the other Q/dO stage are free
           ok = ptx::mbar_wait(&sh->bar_acc, (n - 1) & 1);
@@ -113,24 +177,32 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         ok = ptx::mbar_wait(&sh->bar_q[st], (n >> 1) & 1);
         if (!ok) { fail_at = 3; break; }
+        FA_TRACE(0);
         ptx::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(tmem + kColS, ptx::desc_kmajor(aK, kk), ptx::desc_kmajor(aQ, kk), idesc_s, kk > 0);
+          ptx::mma_ss(tmem + kColS, ptx::desc_at(bK, ptx::koff_kmajor(kk)), ptx::desc_at(bQ, ptx::koff_kmajor(kk)), idesc_s,
+                      kk > 0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(tmem + kColDP, ptx::desc_kmajor(aV, kk), ptx::desc_kmajor(aDO, kk), idesc_s, kk > 0);
+          ptx::mma_ss(tmem + kColDP, ptx::desc_at(bV, ptx::koff_kmajor(kk)), ptx::desc_at(bDO, ptx::koff_kmajor(kk)), idesc_s,
+                      kk > 0);
         ptx::mma_commit(&sh->bar_sdp);
+        FA_TRACE(1);
         ok = ptx::mbar_wait(&sh->bar_pds, n & 1);
         if (!ok) { fail_at = 4; break; }
+        FA_TRACE(2);
         ptx::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
-          ptx::mma_ts(tmem + kColDV, tmem + kColS + kk * 8, ptx::desc_mnmajor(aDO, kk), idesc_acc, (n > 0) || (kk > 0));
+          ptx::mma_ts(tmem + kColDV, tmem + kColS + kk * 8, ptx::desc_at(bDOt, ptx::koff_mnmajor(kk)), idesc_acc,
+                      (n > 0) || (kk > 0));
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
-          ptx::mma_ts(tmem + kColDK, tmem + kColDP + kk * 8, ptx::desc_mnmajor(aQ, kk), idesc_acc, (n > 0) || (kk > 0));
+          ptx::mma_ts(tmem + kColDK, tmem + kColDP + kk * 8, ptx::desc_at(bQt, ptx::koff_mnmajor(kk)), idesc_acc,
+                      (n > 0) || (kk > 0));
         ptx::mma_commit(&sh->bar_acc);
+        FA_TRACE(3);
       }
       if (!ok) give_up(abort_flag, P.status, 3, fail_at);
     }
@@ -159,16 +231,22 @@ __global__ void __launch_bounds__(kThreads, 1)
         float lse2 = 0.f, dl = 0.f;
         if (i < P.seq_q) {
           const float l = P.l[stat_base + i];
-          lse2 = l > 0.f ? fmaf(P.m[stat_base + i], kLog2e, log2f(l)) : 1.0e30f;
+          lse2 = l > 0.f ? fmaf(P.m[stat_base + i], kLog2e, log2f(l)) : 1.0e30f;  // l == 0: p becomes 0
           dl = P.delta[stat_base + i];
         }
-        sh->lse2[st][row] = lse2;
+        sh->nlse2[st][row] = ptx::kRoundLog2 - lse2;  // probabilities come out pre-scaled for pack_bf16_trunc
         sh->delta[st][row] = dl;
         if (MK == FLEXATTN_MASK_DOCUMENT) sh->doc[st][row] = (i < P.seq_q) ? doc[i] : -1;
         ptx::named_bar_sync(1, 128);
       }
-      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_sdp, n & 1));
-      if (!ok) { fail_at = 10; break; }
+      if (tid == 0) FA_TRACE(8);
+      // a failed wait never leaves the loop early: every thread keeps executing the same named barriers
+      if (ok) {
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_sdp, n & 1));
+        if (!ok) fail_at = 10;
+      }
+      if (!ok) continue;
+      if (tid == 0) FA_TRACE(9);
       ptx::tc_fence_after();
       const float abase = slope2 * (float)(j - i0);  // ALiBi bias = slope * (j - i), i = i0 + column
 #pragma unroll
@@ -183,46 +261,26 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::tmem_ld_acquire(sr[1]);
         ptx::tmem_ld_acquire(pr[0]);
         ptx::tmem_ld_acquire(pr[1]);
+        if (tid == 0) FA_TRACE(10 + 2 * half);
         uint32_t pk_p[32], pk_ds[32];
-#pragma unroll
-        for (int c = 0; c < 64; c += 2) {
-          float p2[2], ds2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int cc = half * 64 + c + u;  // column inside the tile = query row offset
-            const float s = __uint_as_float(sr[(c + u) >> 5][(c + u) & 31]);
-            const float dp = __uint_as_float(pr[(c + u) >> 5][(c + u) & 31]);
-            float x2, dsig = 1.f;
-            if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
-              x2 = fmaf(s, c2, fmaf(-slope2, (float)cc, abase));
-            } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
-              const float th = ptx::tanh_approx(s * csc);
-              x2 = capl2 * th;
-              dsig = fmaf(-th, th, 1.f);
-            } else {
-              x2 = s * c2;
-            }
-            float p = ptx::ex2(x2 - sh->lse2[st][cc]);
-            if (partial) {
-              const int i = i0 + cc;
-              const int di = (MK == FLEXATTN_MASK_DOCUMENT) ? sh->doc[st][cc] : 0;
-              const bool keep = (i < P.seq_q) && mask_keep<MK>(i, j, P.window, P.stride, di, dj);
-              p = keep ? p : 0.f;
-            }
-            float d = p * (dp - sh->delta[st][cc]);
-            if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) d *= dsig;
-            p2[u] = p;
-            ds2[u] = d;
-          }
-          pk_p[c >> 1] = ptx::pack_bf16(p2[0], p2[1]);
-          pk_ds[c >> 1] = ptx::pack_bf16(ds2[0], ds2[1]);
-        }
+        // ALiBi bias = slope * (j - i) with i = i0 + half * 64 + column
+        const float abase_h = abase - slope2 * (float)(half * 64);
+        if (partial)
+          dkv_half_math<SK, MK, true>(sr, pr, pk_p, pk_ds, &sh->nlse2[st][half * 64], &sh->delta[st][half * 64],
+                                      &sh->doc[st][half * 64], i0 + half * 64, j, dj, P.seq_q, P.window, P.stride, c2,
+                                      slope2, abase_h, capl2, csc);
+        else
+          dkv_half_math<SK, MK, false>(sr, pr, pk_p, pk_ds, &sh->nlse2[st][half * 64], &sh->delta[st][half * 64],
+                                       &sh->doc[st][half * 64], i0 + half * 64, j, dj, P.seq_q, P.window, P.stride, c2,
+                                       slope2, abase_h, capl2, csc);
         ptx::tmem_st32(lane_base + kColS + half * 32, pk_p);
         ptx::tmem_st32(lane_base + kColDP + half * 32, pk_ds);
+        if (tid == 0) FA_TRACE(11 + 2 * half);
       }
       ptx::tmem_wait_st();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&sh->bar_pds);
+      if (tid == 0) FA_TRACE(14);
     }
 
     if (ok && n_tiles > 0) {

@@ -5,7 +5,8 @@
 // two-stage ring, and per kv tile
 //
 //   S  = Q K^T, dP = dO V^T         tcgen05.mma, f32 accumulators in tensor memory (128 + 128 columns)
-//   dS = P o (dP - delta) o sigma'  in registers, thread t = query row t; P is rebuilt from (l, m) as
+//   dS = P o (dP - delta) o sigma'  in registers by two warpgroups: threads t and t + 128 own query row t and
+//                                   one 64-column half of the tile each; P is rebuilt from (l, m) as
 //                                   exp2(x2 - (m log2e + log2 l)); written back as packed bf16 over S
 //   dQ += dS K                      tcgen05.mma, A = dS from tensor memory, B = the same K tile read
 //                                   MN-major; dQ (D columns) stays in tensor memory across kv tiles
@@ -16,13 +17,57 @@
 namespace flexattn {
 namespace {
 
-constexpr int kThreads = 160;
+constexpr int kThreads = 288;   // warps 0-3 and 4-7: element-wise warpgroups; warp 8: TMA + MMA issue
+constexpr int kCtrlWarp = 8;
 
 struct DqSmem {
   uint64_t bar_q, bar_kv[2], bar_sdp, bar_ds, bar_dq;
   uint32_t tmem_base;
   int32_t doc[2][kTile];
 };
+
+// This thread's 64 columns (keys j_first .. j_first+63) of its query row: raw S and dP in, packed bf16 dS out.
+// nlse2 = log2(1 + 2^-9) - (m log2e + log2 l) (pre-scaling for pack_bf16_trunc) and delta belong to the row.  The mask functor is compiled in only for partial
+// tiles.
+template <int SK, int MK, bool kPartial>
+__device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const uint32_t (&pr)[2][32],
+                                             uint32_t (&pk)[32], float nlse2, float delta,
+                                             const int32_t* __restrict__ s_doc, int i, int di, int j_first, int seq_k,
+                                             int window, int stride, float c2, float slope2, float abase, float capl2,
+                                             float csc) {
+  const float bias0 = abase + nlse2;  // ALiBi: slope * (j_first - i), folded with the row's -lse2
+#pragma unroll
+  for (int c = 0; c < 64; c += 2) {
+    float dv[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int cc = c + u;
+      const float s = __uint_as_float(sr[cc >> 5][cc & 31]);
+      const float dp = __uint_as_float(pr[cc >> 5][cc & 31]);
+      float arg, dsig = 1.f;
+      if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
+        arg = fmaf(s, c2, fmaf(slope2, (float)cc, bias0));
+      } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+        const float th = ptx::tanh_approx(s * csc);
+        arg = fmaf(capl2, th, nlse2);
+        dsig = fmaf(-th, th, 1.f);
+      } else {
+        arg = fmaf(s, c2, nlse2);
+      }
+      float p = ptx::ex2(arg);
+      if constexpr (kPartial) {
+        const int j = j_first + cc;
+        const int dj = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[cc] : 0;
+        const bool keep = (j < seq_k) && mask_keep<MK>(i, j, window, stride, di, dj);
+        p = keep ? p : 0.f;
+      }
+      float d = p * (dp - delta);
+      if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) d *= dsig;
+      dv[u] = d;
+    }
+    pk[c >> 1] = ptx::pack_bf16_trunc(dv[0], dv[1]);
+  }
+}
 
 template <int D, int SK, int MK>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -55,11 +100,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::mbar_init(&sh->bar_kv[0], 1);
     ptx::mbar_init(&sh->bar_kv[1], 1);
     ptx::mbar_init(&sh->bar_sdp, 1);
-    ptx::mbar_init(&sh->bar_ds, 128);
+    ptx::mbar_init(&sh->bar_ds, 256);
     ptx::mbar_init(&sh->bar_dq, 1);
     ptx::fence_barrier_init();
   }
-  if (warp == 4) {
+  if (warp == kCtrlWarp) {
     ptx::tmem_alloc(&sh->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -68,7 +113,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   ptx::tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
 
-  if (warp == 4) {
+  if (warp == kCtrlWarp) {
     if (lane == 0 && n_tiles > 0) {
       bool ok = true;
       int fail_at = 1;
@@ -87,11 +132,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       constexpr uint32_t idesc_s = ptx::make_idesc(128, 128, false);
       constexpr uint32_t idesc_dq = ptx::make_idesc(128, D, true);
-      const uint32_t aQ = ptx::smem_u32(sQ), aDO = ptx::smem_u32(sDO);
+      const ptx::DescBase bQ = ptx::base_kmajor(ptx::smem_u32(sQ)), bDO = ptx::base_kmajor(ptx::smem_u32(sDO));
       ok = ptx::mbar_wait(&sh->bar_q, 0);
       for (int n = 0; n < n_tiles && ok; ++n) {
         const int st = n & 1;
-        const uint32_t aK = ptx::smem_u32(sK + st * kTileBytes), aV = ptx::smem_u32(sV + st * kTileBytes);
+        const ptx::DescBase bK = ptx::base_kmajor(ptx::smem_u32(sK + st * kTileBytes)),
+                            bV = ptx::base_kmajor(ptx::smem_u32(sV + st * kTileBytes)),
+                            bKt = ptx::base_mnmajor(ptx::smem_u32(sK + st * kTileBytes));
         if (n > 0) {
           // dQ MMA of the previous tile done: S/dP columns and the other K/V stage are free
           ok = ptx::mbar_wait(&sh->bar_dq, (n - 1) & 1);
@@ -112,26 +159,30 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(tmem + kColS, ptx::desc_kmajor(aQ, kk), ptx::desc_kmajor(aK, kk), idesc_s, kk > 0);
+          ptx::mma_ss(tmem + kColS, ptx::desc_at(bQ, ptx::koff_kmajor(kk)), ptx::desc_at(bK, ptx::koff_kmajor(kk)), idesc_s,
+                      kk > 0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(tmem + kColDP, ptx::desc_kmajor(aDO, kk), ptx::desc_kmajor(aV, kk), idesc_s, kk > 0);
+          ptx::mma_ss(tmem + kColDP, ptx::desc_at(bDO, ptx::koff_kmajor(kk)), ptx::desc_at(bV, ptx::koff_kmajor(kk)), idesc_s,
+                      kk > 0);
         ptx::mma_commit(&sh->bar_sdp);
         ok = ptx::mbar_wait(&sh->bar_ds, n & 1);
         if (!ok) { fail_at = 4; break; }
         ptx::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
-          ptx::mma_ts(tmem + kColDQ, tmem + kColS + kk * 8, ptx::desc_mnmajor(aK, kk), idesc_dq, (n > 0) || (kk > 0));
+          ptx::mma_ts(tmem + kColDQ, tmem + kColS + kk * 8, ptx::desc_at(bKt, ptx::koff_mnmajor(kk)), idesc_dq,
+                      (n > 0) || (kk > 0));
         ptx::mma_commit(&sh->bar_dq);
       }
       if (!ok) give_up(abort_flag, P.status, 2, fail_at);
     }
   } else {
-    const int row = tid;
+    const int row = tid & 127;         // query row inside the tile = TMEM lane
+    const int half = tid >> 7;         // which 64-column half of every tile this thread handles
     const int i = qt * kTile + row;
     const bool row_ok = i < P.seq_q;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float c2 = P.sm_scale * kLog2e;
     const float slope2 = (SK == FLEXATTN_SCORE_ALIBI) ? P.alibi_slopes[h] * kLog2e : 0.f;
     const float capl2 = P.cap * kLog2e;
@@ -153,15 +204,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       const bool partial = !(kt >= rm.z && kt < rm.w);
       if (MK == FLEXATTN_MASK_DOCUMENT && partial) {
         const int j = j0 + row;
-        sh->doc[n & 1][row] = (j < P.seq_k) ? doc[j] : -1;
-        ptx::named_bar_sync(1, 128);
+        if (half == 0) sh->doc[n & 1][row] = (j < P.seq_k) ? doc[j] : -1;
+        ptx::named_bar_sync(1, 256);
       }
-      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_sdp, n & 1));
-      if (!ok) { fail_at = 10; break; }
+      // a failed wait never leaves the loop early: every thread keeps executing the same named barriers
+      if (ok) {
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_sdp, n & 1));
+        if (!ok) fail_at = 10;
+      }
+      if (!ok) continue;
       ptx::tc_fence_after();
       const float abase = slope2 * (float)(j0 - i);
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         uint32_t sr[2][32], pr[2][32];
         ptx::tmem_ld32(lane_base + kColS + half * 64, sr[0]);
         ptx::tmem_ld32(lane_base + kColS + half * 64 + 32, sr[1]);
@@ -173,37 +227,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::tmem_ld_acquire(pr[0]);
         ptx::tmem_ld_acquire(pr[1]);
         uint32_t pk[32];
-#pragma unroll
-        for (int c = 0; c < 64; c += 2) {
-          float ds2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int cc = half * 64 + c + u;  // column inside the tile
-            const float s = __uint_as_float(sr[(c + u) >> 5][(c + u) & 31]);
-            const float dp = __uint_as_float(pr[(c + u) >> 5][(c + u) & 31]);
-            float x2, dsig = 1.f;
-            if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
-              x2 = fmaf(s, c2, fmaf(slope2, (float)cc, abase));
-            } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
-              const float th = ptx::tanh_approx(s * csc);
-              x2 = capl2 * th;
-              dsig = fmaf(-th, th, 1.f);
-            } else {
-              x2 = s * c2;
-            }
-            float p = ptx::ex2(x2 - lse2);
-            if (partial) {
-              const int j = j0 + cc;
-              const int dj = (MK == FLEXATTN_MASK_DOCUMENT) ? sh->doc[n & 1][cc] : 0;
-              const bool keep = (j < P.seq_k) && mask_keep<MK>(i, j, P.window, P.stride, di, dj);
-              p = keep ? p : 0.f;
-            }
-            float d = p * (dp - delta);
-            if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) d *= dsig;
-            ds2[u] = d;
-          }
-          pk[c >> 1] = ptx::pack_bf16(ds2[0], ds2[1]);
-        }
+        const float abase_h = abase + slope2 * (float)(half * 64);
+        if (partial)
+          dq_half_math<SK, MK, true>(sr, pr, pk, ptx::kRoundLog2 - lse2, delta, &sh->doc[n & 1][half * 64], i, di, j0 + half * 64,
+                                     P.seq_k, P.window, P.stride, c2, slope2, abase_h, capl2, csc);
+        else
+          dq_half_math<SK, MK, false>(sr, pr, pk, ptx::kRoundLog2 - lse2, delta, &sh->doc[n & 1][half * 64], i, di, j0 + half * 64,
+                                      P.seq_k, P.window, P.stride, c2, slope2, abase_h, capl2, csc);
         ptx::tmem_st32(lane_base + kColS + half * 32, pk);
       }
       ptx::tmem_wait_st();
@@ -220,7 +250,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       __nv_bfloat16* out = static_cast<__nv_bfloat16*>(P.dq) + grow * D;
       const float sc = P.sm_scale;
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
         uint32_t r[32];
         if (n_tiles > 0) {
           ptx::tmem_ld32(lane_base + kColDQ + c0, r);
@@ -249,7 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kCtrlWarp) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
   }

@@ -65,6 +65,7 @@ struct DevParams {
   const int4* row_map;  // [rows][n_qt]
   const int4* col_map;  // [rows][n_kt]
   int32_t* status;
+  long long* trace;  // per-phase cycle stamps of one CTA; only written by builds with FLEXATTN_TRACE
   int batch, heads, seq_q, seq_k, head_dim;
   int n_qt, n_kt, map_rows, doc_stride;
   int window, stride;
@@ -133,7 +134,8 @@ cudaError_t launch_simt_fwd(cudaStream_t st, const DevParams& d, int dtype, int 
 cudaError_t launch_simt_dq(cudaStream_t st, const DevParams& d, int dtype, int score, int mask);
 cudaError_t launch_simt_dkv(cudaStream_t st, const DevParams& d, int dtype, int score, int mask);
 // tensor-core (tcgen05) kernels: bf16, D in {64,128}
-int launch_sm100_fwd(cudaStream_t st, const DevParams& d, int score, int mask);
+int launch_sm100_fwd(cudaStream_t st, const DevParams& d, int score, int mask);       // one score tile in flight, 2 CTAs/SM
+int launch_sm100_fwd_pipe(cudaStream_t st, const DevParams& d, int score, int mask);  // three score tiles in flight, 1 CTA/SM
 int launch_sm100_dq(cudaStream_t st, const DevParams& d, int score, int mask);
 int launch_sm100_dkv(cudaStream_t st, const DevParams& d, int score, int mask);
 

@@ -16,6 +16,16 @@
 // O D columns (256 allocated).  Two CTAs fit on an SM, so one CTA's softmax overlaps the other's MMAs.
 #include "sm100.cuh"
 
+#ifdef FLEXATTN_TRACE
+#define FA_TRACE(slot)                                                          \
+  do {                                                                          \
+    if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64)     \
+      P.trace[n * 16 + (slot)] = clock64();                                     \
+  } while (0)
+#else
+#define FA_TRACE(slot)
+#endif
+
 namespace flexattn {
 namespace {
 
@@ -118,13 +128,15 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
         ptx::tma_load_3d(sV + p * ptx::kPanelBytes, &tm_v, &sh->bar_v, p * 64, rm.x * kTile, bh);
       constexpr uint32_t idesc_qk = ptx::make_idesc(128, 128, false);
       constexpr uint32_t idesc_pv = ptx::make_idesc(128, D, true);
-      const uint32_t aQ = ptx::smem_u32(sQ), aK = ptx::smem_u32(sK), aV = ptx::smem_u32(sV);
+      const ptx::DescBase bQ = ptx::base_kmajor(ptx::smem_u32(sQ)), bK = ptx::base_kmajor(ptx::smem_u32(sK)),
+                          bV = ptx::base_mnmajor(ptx::smem_u32(sV));
       ok = ptx::mbar_wait(&sh->bar_q, 0);
       int fail_at = 1;
       for (int n = 0; n < n_tiles && ok; ++n) {
         const uint32_t par = n & 1;
         ok = ptx::mbar_wait(&sh->bar_k, par);
         if (!ok) { fail_at = 2; break; }
+        FA_TRACE(0);
         if (n > 0) {
           // P V of the previous tile done: S/P columns and the V buffer are free again
           ok = ptx::mbar_wait(&sh->bar_pv, par ^ 1);
@@ -134,13 +146,17 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
           for (int p = 0; p < kPanels; ++p)
             ptx::tma_load_3d(sV + p * ptx::kPanelBytes, &tm_v, &sh->bar_v, p * 64, (rm.x + n) * kTile, bh);
         }
+        FA_TRACE(1);
         ptx::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(tmem + kColS, ptx::desc_kmajor(aQ, kk), ptx::desc_kmajor(aK, kk), idesc_qk, kk > 0);
+          ptx::mma_ss(tmem + kColS, ptx::desc_at(bQ, ptx::koff_kmajor(kk)), ptx::desc_at(bK, ptx::koff_kmajor(kk)), idesc_qk,
+                      kk > 0);
         ptx::mma_commit(&sh->bar_s);
+        FA_TRACE(2);
         ok = ptx::mbar_wait(&sh->bar_s, par);  // Q K^T done: the K buffer is free
         if (!ok) { fail_at = 4; break; }
+        FA_TRACE(3);
         if (n + 1 < n_tiles) {
           ptx::mbar_arrive_expect_tx(&sh->bar_k, kTileBytes);
 #pragma unroll
@@ -149,13 +165,17 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
         }
         ok = ptx::mbar_wait(&sh->bar_v, par);
         if (!ok) { fail_at = 5; break; }
+        FA_TRACE(4);
         ok = ptx::mbar_wait(&sh->bar_p, par);
         if (!ok) { fail_at = 6; break; }
+        FA_TRACE(5);
         ptx::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
-          ptx::mma_ts(tmem + kColO, tmem + kColS + kk * 8, ptx::desc_mnmajor(aV, kk), idesc_pv, (n > 0) || (kk > 0));
+          ptx::mma_ts(tmem + kColO, tmem + kColS + kk * 8, ptx::desc_at(bV, ptx::koff_mnmajor(kk)), idesc_pv,
+                      (n > 0) || (kk > 0));
         ptx::mma_commit(&sh->bar_pv);
+        FA_TRACE(6);
       }
       if (!ok) give_up(abort_flag, P.status, 1, fail_at);
     }
@@ -183,8 +203,13 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
         sh->doc[par][row] = (j < P.seq_k) ? doc[j] : -1;
         ptx::named_bar_sync(1, 128);
       }
-      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_s, par));
-      if (!ok) { fail_at = 10; break; }
+      // a failed wait never leaves the loop early: every thread keeps executing the same named barriers
+      if (ok) {
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_s, par));
+        if (!ok) fail_at = 10;
+      }
+      if (!ok) continue;
+      if (tid == 0) FA_TRACE(8);
       ptx::tc_fence_after();
       float x[kTile];
       {
@@ -199,11 +224,29 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
           for (int c = 0; c < 32; ++c) x[q4 * 32 + c] = __uint_as_float(xr[q4][c]);
         }
       }
-      float tmax;
-      if (partial)
+      if (tid == 0) FA_TRACE(9);
+      // xs: factor still to be applied to x inside the exp2 argument (the plain-score fast path keeps the raw
+      // scores and folds sm_scale*log2e into the FMA that also subtracts the running max)
+      float tmax, xs = 1.0f;
+      if (partial) {
         tmax = score_tile<SK, MK, true>(x, i, j0, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di, sh->doc[par]);
-      else
+      } else if constexpr (SK != FLEXATTN_SCORE_NONE) {
         tmax = score_tile<SK, MK, false>(x, i, j0, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di, sh->doc[par]);
+      } else {
+        float mx[4] = {x[0], x[1], x[2], x[3]};
+#pragma unroll
+        for (int c = 4; c < kTile; c += 8) {
+          mx[0] = ptx::max3(mx[0], x[c], x[c + 1]);
+          mx[1] = ptx::max3(mx[1], x[c + 2], x[c + 3]);
+          if (c + 4 < kTile) {
+            mx[2] = ptx::max3(mx[2], x[c + 4], x[c + 5]);
+            mx[3] = ptx::max3(mx[3], x[c + 6], x[c + 7]);
+          }
+        }
+        tmax = ptx::max3(mx[0], mx[1], fmaxf(mx[2], mx[3])) * c2;   // c2 > 0: scaling commutes with max
+        xs = c2;
+      }
+      if (tid == 0) FA_TRACE(10);
       m_true = fmaxf(m_true, tmax);
       const float m_cand = fmaxf(m_ref, tmax);
       if (__any_sync(0xffffffffu, (m_cand - m_ref) > kLazyRescale)) {
@@ -212,7 +255,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
         m_ref = m_cand;
         if (n > 0) {
           ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_pv, par ^ 1));
-          if (!ok) { fail_at = 11; break; }
+          if (!ok) { fail_at = 11; continue; }
           ptx::tc_fence_after();
 #pragma unroll 1
           for (int c0 = 0; c0 < D; c0 += 32) {
@@ -227,22 +270,27 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
           ptx::tmem_wait_st();
         }
       }
+      if (tid == 0) FA_TRACE(11);
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      const float nm = ptx::kRoundLog2 - m_ref;
 #pragma unroll
       for (int c0 = 0; c0 < kTile; c0 += 64) {
         uint32_t pk[32];
 #pragma unroll
         for (int c = 0; c < 64; c += 2) {
-          const float p0 = ptx::ex2(x[c0 + c] - m_ref), p1 = ptx::ex2(x[c0 + c + 1] - m_ref);
+          // pre-scaled by (1 + 2^-9) for pack_bf16_trunc; the factor cancels in o = acc / l
+          const float p0 = ptx::ex2(fmaf(x[c0 + c], xs, nm)), p1 = ptx::ex2(fmaf(x[c0 + c + 1], xs, nm));
           ls[(c >> 1) & 3] += p0 + p1;
-          pk[c >> 1] = ptx::pack_bf16(p0, p1);
+          pk[c >> 1] = ptx::pack_bf16_trunc(p0, p1);
         }
         ptx::tmem_st32(lane_base + kColS + (c0 >> 1), pk);
       }
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      if (tid == 0) FA_TRACE(12);
       ptx::tmem_wait_st();
       ptx::tc_fence_before();
       ptx::mbar_arrive(&sh->bar_p);
+      if (tid == 0) FA_TRACE(13);
     }
 
     if (ok && n_tiles > 0) {
@@ -278,7 +326,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
         }
       }
       if (i < P.seq_q) {
-        P.l[grow] = l * ptx::ex2(m_ref - m_true);
+        P.l[grow] = l * ptx::ex2(m_ref - m_true) * ptx::kRoundInv;
         P.m[grow] = m_true * kLn2;
       }
     } else if (lane == 0) {

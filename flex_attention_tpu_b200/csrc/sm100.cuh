@@ -177,6 +177,31 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int kstep /
   return make_smem_desc(tile_addr + (uint32_t)kstep * 2048u, kPanelBytes, 1024);
 }
 
+// The MMA-issuing thread is a single thread: every integer instruction it spends building a descriptor
+// delays the next tcgen05.mma by several cycles, and a 128x128x16 MMA is only 64 cycles of tensor work.
+// So descriptors are split into a per-buffer base (built once) and a per-K-step byte offset that is a
+// compile-time constant: one 32-bit add per descriptor.
+struct DescBase {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ DescBase desc_base(uint32_t tile_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  DescBase b;
+  b.lo = ((tile_addr >> 4) & 0x3fffu) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+  b.hi = ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | ((uint32_t)kSwizzle128B << 29);
+  return b;
+}
+__device__ __forceinline__ DescBase base_kmajor(uint32_t tile_addr) { return desc_base(tile_addr, 16, 1024); }
+__device__ __forceinline__ DescBase base_mnmajor(uint32_t tile_addr) { return desc_base(tile_addr, kPanelBytes, 1024); }
+__device__ __forceinline__ uint64_t desc_at(const DescBase& b, uint32_t byte_off) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(b.lo + (byte_off >> 4)), "r"(b.hi));
+  return d;
+}
+__host__ __device__ constexpr uint32_t koff_kmajor(int kstep) {
+  return (uint32_t)(kstep >> 2) * kPanelBytes + (uint32_t)(kstep & 3) * 32u;
+}
+__host__ __device__ constexpr uint32_t koff_mnmajor(int kstep) { return (uint32_t)kstep * 2048u; }
+
 // Instruction descriptor for kind::f16 with bf16 operands and f32 accumulation:
 // [4,6) D format (1 = f32), [7,10) A format (1 = bf16), [10,13) B format (1 = bf16),
 // bit 15 A major (0 = K), bit 16 B major (0 = K, 1 = MN), [17,23) N >> 3, [24,29) M >> 4.
@@ -214,10 +239,42 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+// cvt.rn.bf16x2.f32 runs on the special-function pipe at a quarter of the FP32 rate (measured: 8 cycles per
+// warp instruction, the same pipe and cost as ex2), so on the hot path it would double the load of the unit
+// that already bounds the softmax.  The hot path therefore packs by TRUNCATION (one byte-permute on the
+// integer pipe) of values that were pre-multiplied by (1 + 2^-9): adding between a quarter and half a bf16
+// ulp before dropping the low mantissa bits is rounding to nearest up to a bias of about -2^-11.  The
+// pre-multiplication is free: probabilities get it by adding kRoundLog2 = log2(1 + 2^-9) to the exp2
+// argument, products of such a probability inherit it.
+constexpr float kRoundLog2 = 0.0028150156f;
+constexpr float kRoundInv = 1.0f / 1.001953125f;
+__device__ __forceinline__ uint32_t pack_bf16_trunc(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// exp2 on the FMA pipe (no special-function unit): floor/fraction split with the 1.5*2^23 trick, a cubic
+// for 2^f on [0,1) (max relative error 8.6e-5, below the 2^-9 rounding of a bf16 probability) and the
+// integer part added straight into the exponent field.  Valid for x <= 100; anything below -125 returns
+// about 2^-125 (used for masked logits, which must come out as "almost zero", never NaN).  Mixing this
+// with ex2.approx element by element relieves the special-function unit, which is the tighter limit of
+// the softmax (16 results per clock per SM against 128 FMA lanes).
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -125.0f);
+  const float t = __fadd_rd(x, 12582912.0f);        // low mantissa bits now hold floor(x)
+  const float f = x - (t - 12582912.0f);            // fractional part in [0, 1)
+  float p = fmaf(f, 0.07706704f, 0.22764499f);
+  p = fmaf(p, f, 0.69511679f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 __device__ __forceinline__ float tanh_approx(float x) {
   float y;
