@@ -7,12 +7,15 @@
 // the layout the next MMA wants as its A operand:
 //
 //   S^T  = K Q^T, dP^T = V dO^T      tcgen05.mma, f32 accumulators (128 + 128 TMEM columns)
-//   P^T, dS^T                        in registers; thread t = key row t, columns = query positions, whose
-//                                    statistics (m log2e + log2 l, delta) are read from shared memory;
-//                                    written back as packed bf16 over S^T / dP^T
+//   P^T, dS^T                        in registers; thread = key row, columns = query positions, whose statistics
+//                                    (m log2e + log2 l, delta) are read from shared memory; written back as
+//                                    packed bf16 over S^T / dP^T
 //   dV += P^T dO ; dK += dS^T Q      tcgen05.mma, A from tensor memory, B = the dO / Q tile read MN-major
 //
-// dK, dV (D columns each) stay in tensor memory across q tiles: 512 columns in total, one CTA per SM.
+// Every tile is processed as two independent half-tile chains (query columns 0..63 and 64..127), each with
+// its own warpgroup and barriers: while one chain's warpgroup does its element-wise work the tensor core
+// runs the other chain's MMAs, so neither side idles.  dK, dV (D columns each) stay in tensor memory
+// across q tiles: 512 columns in total, one CTA per SM.
 #include "sm100.cuh"
 
 #ifdef FLEXATTN_TRACE
@@ -28,10 +31,11 @@
 namespace flexattn {
 namespace {
 
-constexpr int kThreads = 160;
+constexpr int kThreads = 320;  // warps 0-3, 4-7: element-wise warpgroups (one per half-tile chain); 8: MMA; 9: TMA
+constexpr int kMmaWarp = 8, kTmaWarp = 9;
 
 struct DkvSmem {
-  uint64_t bar_kv, bar_q[2], bar_sdp, bar_pds, bar_acc;
+  uint64_t bar_kv, bar_q[2], bar_free[2], bar_sdp[2], bar_pds[2], bar_acc[2], bar_zero;
   uint32_t tmem_base;
   alignas(16) float nlse2[2][kTile];  // -(m log2e + log2 l) of the query rows of the tile in flight
   alignas(16) float delta[2][kTile];
@@ -98,6 +102,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   constexpr uint32_t kTileBytes = kPanels * ptx::kPanelBytes;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 384;
+  constexpr uint32_t kRowsHalfBytes = 64 * 128;  // 64 rows of a K-major panel
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -111,20 +116,23 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int kt = blockIdx.x;  // early kv tiles see the most query tiles under a causal mask: run them first
   const int bh = blockIdx.y, b = bh / P.heads, h = bh % P.heads;
   const int4 cm = P.col_map[(size_t)(P.map_rows > 1 ? b : 0) * P.n_kt + kt];
-  const int n_tiles = cm.y - cm.x;
+  const int N = cm.y - cm.x;
 
   if (*reinterpret_cast<volatile int*>(abort_flag) != 0) return;
 
   if (tid == 0) {
     ptx::mbar_init(&sh->bar_kv, 1);
-    ptx::mbar_init(&sh->bar_q[0], 1);
-    ptx::mbar_init(&sh->bar_q[1], 1);
-    ptx::mbar_init(&sh->bar_sdp, 1);
-    ptx::mbar_init(&sh->bar_pds, 128);
-    ptx::mbar_init(&sh->bar_acc, 1);
+    ptx::mbar_init(&sh->bar_zero, 256);
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(&sh->bar_q[s], 1);
+      ptx::mbar_init(&sh->bar_free[s], 1);
+      ptx::mbar_init(&sh->bar_sdp[s], 1);
+      ptx::mbar_init(&sh->bar_pds[s], 128);
+      ptx::mbar_init(&sh->bar_acc[s], 1);
+    }
     ptx::fence_barrier_init();
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     ptx::tmem_alloc(&sh->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -133,84 +141,120 @@ __global__ void __launch_bounds__(kThreads, 1)
   ptx::tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
 
-  if (warp == 4) {
-    if (lane == 0 && n_tiles > 0) {
+  if (warp == kTmaWarp) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && N > 0) {
       bool ok = true;
-      int fail_at = 1;
       ptx::prefetch_tensormap(&tm_q);
       ptx::prefetch_tensormap(&tm_do);
       ptx::prefetch_tensormap(&tm_k);
       ptx::prefetch_tensormap(&tm_v);
       ptx::mbar_arrive_expect_tx(&sh->bar_kv, 2 * kTileBytes);
-      ptx::mbar_arrive_expect_tx(&sh->bar_q[0], 2 * kTileBytes);
 #pragma unroll
       for (int p = 0; p < kPanels; ++p) {
         ptx::tma_load_3d(sK + p * ptx::kPanelBytes, &tm_k, &sh->bar_kv, p * 64, kt * kTile, bh);
         ptx::tma_load_3d(sV + p * ptx::kPanelBytes, &tm_v, &sh->bar_kv, p * 64, kt * kTile, bh);
-        ptx::tma_load_3d(sQ + p * ptx::kPanelBytes, &tm_q, &sh->bar_q[0], p * 64, cm.x * kTile, bh);
-        ptx::tma_load_3d(sDO + p * ptx::kPanelBytes, &tm_do, &sh->bar_q[0], p * 64, cm.x * kTile, bh);
       }
-      constexpr uint32_t idesc_s = ptx::make_idesc(128, 128, false);
-      constexpr uint32_t idesc_acc = ptx::make_idesc(128, D, true);
-      const ptx::DescBase bK = ptx::base_kmajor(ptx::smem_u32(sK)), bV = ptx::base_kmajor(ptx::smem_u32(sV));
-      ok = ptx::mbar_wait(&sh->bar_kv, 0);
-      for (int n = 0; n < n_tiles && ok; ++n) {
+      for (int n = 0; n < N && ok; ++n) {
         const int st = n & 1;
-        const ptx::DescBase bQ = ptx::base_kmajor(ptx::smem_u32(sQ + st * kTileBytes)),
-                            bDO = ptx::base_kmajor(ptx::smem_u32(sDO + st * kTileBytes)),
-                            bQt = ptx::base_mnmajor(ptx::smem_u32(sQ + st * kTileBytes)),
-                            bDOt = ptx::base_mnmajor(ptx::smem_u32(sDO + st * kTileBytes));
-        if (n > 0) {
-          // accumulation MMAs of the previous tile done: S^T/dP^T columns and the other Q/dO stage are free
-          ok = ptx::mbar_wait(&sh->bar_acc, (n - 1) & 1);
-          if (!ok) { fail_at = 2; break; }
+        if (n >= 2) {  // the stage held tile n-2: wait until all of its MMAs have completed
+          ok = ptx::mbar_wait(&sh->bar_free[st], ((n - 2) >> 1) & 1);
+          if (!ok) break;
         }
-        if (n + 1 < n_tiles) {
-          uint8_t* nQ = sQ + (st ^ 1) * kTileBytes;
-          uint8_t* nDO = sDO + (st ^ 1) * kTileBytes;
-          ptx::mbar_arrive_expect_tx(&sh->bar_q[st ^ 1], 2 * kTileBytes);
+        ptx::mbar_arrive_expect_tx(&sh->bar_q[st], 2 * kTileBytes);
 #pragma unroll
-          for (int p = 0; p < kPanels; ++p) {
-            ptx::tma_load_3d(nQ + p * ptx::kPanelBytes, &tm_q, &sh->bar_q[st ^ 1], p * 64, (cm.x + n + 1) * kTile, bh);
-            ptx::tma_load_3d(nDO + p * ptx::kPanelBytes, &tm_do, &sh->bar_q[st ^ 1], p * 64, (cm.x + n + 1) * kTile, bh);
+        for (int p = 0; p < kPanels; ++p) {
+          ptx::tma_load_3d(sQ + st * kTileBytes + p * ptx::kPanelBytes, &tm_q, &sh->bar_q[st], p * 64,
+                           (cm.x + n) * kTile, bh);
+          ptx::tma_load_3d(sDO + st * kTileBytes + p * ptx::kPanelBytes, &tm_do, &sh->bar_q[st], p * 64,
+                           (cm.x + n) * kTile, bh);
+        }
+      }
+      if (!ok) give_up(abort_flag, P.status, 3, 20);
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer: two half-tile chains
+    // Chain c owns query columns [64c, 64c+64) of every tile: S^T_c / dP^T_c (N = 64) -> warpgroup c ->
+    // dV, dK += (P^T_c, dS^T_c) x (dO, Q rows 64c..).  The chains alternate on the tensor core so that one
+    // chain's MMAs run while the other chain's warpgroup does its element-wise work.  dK / dV are zeroed by the
+    // warpgroups first, so every accumulation MMA adds.  (N = 64 MMAs cost as many cycles as N = 128 ones - the
+    // A operand fetch of 128 rows bounds them - so the chains buy overlap at the price of tensor efficiency.)
+    if (lane == 0 && N > 0) {
+      bool ok = true;
+      int fail_at = 1;
+      constexpr uint32_t idesc_s = ptx::make_idesc(128, 64, false);
+      constexpr uint32_t idesc_acc = ptx::make_idesc(128, D, true);
+      const uint32_t aK = ptx::smem_u32(sK), aV = ptx::smem_u32(sV), aQ = ptx::smem_u32(sQ), aDO = ptx::smem_u32(sDO);
+      const ptx::DescBase bK = ptx::base_kmajor(aK), bV = ptx::base_kmajor(aV);
+      auto issue_sdp = [&](int n, int c) {  // S^T_c = K Q_c^T and dP^T_c = V dO_c^T for tile n
+        const uint32_t off = (uint32_t)(n & 1) * kTileBytes + (uint32_t)c * kRowsHalfBytes;
+        const ptx::DescBase bQ = ptx::base_kmajor(aQ + off), bDO = ptx::base_kmajor(aDO + off);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          ptx::mma_ss(tmem + kColS + 64 * c, ptx::desc_at(bK, ptx::koff_kmajor(kk)),
+                         ptx::desc_at(bQ, ptx::koff_kmajor(kk)), idesc_s, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          ptx::mma_ss(tmem + kColDP + 64 * c, ptx::desc_at(bV, ptx::koff_kmajor(kk)),
+                         ptx::desc_at(bDO, ptx::koff_kmajor(kk)), idesc_s, kk > 0);
+        ptx::mma_commit(&sh->bar_sdp[c]);
+      };
+      auto issue_acc = [&](int n, int c) {  // dV += P^T_c dO_c ; dK += dS^T_c Q_c  (four K steps of 16 query rows)
+        const uint32_t off = (uint32_t)(n & 1) * kTileBytes + (uint32_t)c * 4 * 2048u;
+        const ptx::DescBase bQt = ptx::base_mnmajor(aQ + off), bDOt = ptx::base_mnmajor(aDO + off);
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)
+          ptx::mma_ts(tmem + kColDV, tmem + kColS + 64 * c + k4 * 8, ptx::desc_at(bDOt, ptx::koff_mnmajor(k4)),
+                         idesc_acc, 1);
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)
+          ptx::mma_ts(tmem + kColDK, tmem + kColDP + 64 * c + k4 * 8, ptx::desc_at(bQt, ptx::koff_mnmajor(k4)),
+                         idesc_acc, 1);
+        ptx::mma_commit(&sh->bar_acc[c]);
+      };
+      ok = ptx::mbar_wait(&sh->bar_kv, 0) && ptx::mbar_wait(&sh->bar_q[0], 0);
+      if (ok) {
+        ptx::tc_fence_after();
+        issue_sdp(0, 0);
+        issue_sdp(0, 1);
+        ok = ptx::mbar_wait(&sh->bar_zero, 0);  // dK / dV columns zeroed
+        if (!ok) fail_at = 7;
+      }
+      for (int n = 0; n < N && ok; ++n) {
+        const uint32_t par = n & 1;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          ok = ptx::mbar_wait(&sh->bar_pds[c], par);
+          if (!ok) { fail_at = 2 + c; break; }
+          if (c == 0) FA_TRACE(0); else FA_TRACE(3);
+          ptx::tc_fence_after();
+          issue_acc(n, c);
+          if (c == 1) ptx::mma_commit(&sh->bar_free[n & 1]);  // every MMA reading this Q/dO stage is issued
+          if (c == 0) FA_TRACE(1); else FA_TRACE(4);
+          if (n + 1 < N) {
+            if (c == 0) {
+              ok = ptx::mbar_wait(&sh->bar_q[(n + 1) & 1], ((n + 1) >> 1) & 1);
+              if (!ok) { fail_at = 4; break; }
+            }
+            // chain c's accumulation MMAs must have consumed P^T_c / dS^T_c before the next S^T_c / dP^T_c land
+            ok = ptx::mbar_wait(&sh->bar_acc[c], par);
+            if (!ok) { fail_at = 5 + c; break; }
+            ptx::tc_fence_after();
+            issue_sdp(n + 1, c);
+            if (c == 0) FA_TRACE(2); else FA_TRACE(5);
           }
         }
-        ok = ptx::mbar_wait(&sh->bar_q[st], (n >> 1) & 1);
-        if (!ok) { fail_at = 3; break; }
-        FA_TRACE(0);
-        ptx::tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(tmem + kColS, ptx::desc_at(bK, ptx::koff_kmajor(kk)), ptx::desc_at(bQ, ptx::koff_kmajor(kk)), idesc_s,
-                      kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(tmem + kColDP, ptx::desc_at(bV, ptx::koff_kmajor(kk)), ptx::desc_at(bDO, ptx::koff_kmajor(kk)), idesc_s,
-                      kk > 0);
-        ptx::mma_commit(&sh->bar_sdp);
-        FA_TRACE(1);
-        ok = ptx::mbar_wait(&sh->bar_pds, n & 1);
-        if (!ok) { fail_at = 4; break; }
-        FA_TRACE(2);
-        ptx::tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          ptx::mma_ts(tmem + kColDV, tmem + kColS + kk * 8, ptx::desc_at(bDOt, ptx::koff_mnmajor(kk)), idesc_acc,
-                      (n > 0) || (kk > 0));
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          ptx::mma_ts(tmem + kColDK, tmem + kColDP + kk * 8, ptx::desc_at(bQt, ptx::koff_mnmajor(kk)), idesc_acc,
-                      (n > 0) || (kk > 0));
-        ptx::mma_commit(&sh->bar_acc);
-        FA_TRACE(3);
       }
       if (!ok) give_up(abort_flag, P.status, 3, fail_at);
     }
   } else {
-    const int row = tid;
-    const int j = kt * kTile + row;  // global key position
+    // ------------------------------------------------------------------ element-wise warpgroups (chain = tid / 128)
+    const int row = tid & 127;        // key row inside the tile = TMEM lane
+    const int chain = tid >> 7;       // which 64 query columns of every tile this warpgroup handles
+    const int j = kt * kTile + row;   // global key position
     const bool row_ok = j < P.seq_k;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t colS = kColS + 64 * chain, colDP = kColDP + 64 * chain;
     const float c2 = P.sm_scale * kLog2e;
     const float slope2 = (SK == FLEXATTN_SCORE_ALIBI) ? P.alibi_slopes[h] * kLog2e : 0.f;
     const float capl2 = P.cap * kLog2e;
@@ -221,84 +265,94 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool ok = true;
     int fail_at = 0;
 
-    for (int n = 0; n < n_tiles; ++n) {
+    {  // zero the accumulators (warpgroup 0: dK, warpgroup 1: dV): every accumulation MMA adds
+      uint32_t z[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) z[c] = 0u;
+      const uint32_t col = chain ? kColDV : kColDK;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) ptx::tmem_st32(lane_base + col + c0, z);
+      ptx::tmem_wait_st();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(&sh->bar_zero);
+    }
+
+    for (int n = 0; n < N; ++n) {
       const int st = n & 1;
-      const int qt = cm.x + n, i0 = qt * kTile;
+      const int qt = cm.x + n, i0 = qt * kTile + 64 * chain;  // first query position of this chain's columns
       const bool partial = !(qt >= cm.z && qt < cm.w);
-      {
-        // statistics of query row i0 + row for this tile (thread t stages row t, everyone reads all 128)
+      if (row < 64) {
+        // statistics of this chain's 64 query rows (threads 0..63 of the warpgroup stage one row each)
         const int i = i0 + row;
-        float lse2 = 0.f, dl = 0.f;
+        float nl = ptx::kRoundLog2, dl = 0.f;
         if (i < P.seq_q) {
           const float l = P.l[stat_base + i];
-          lse2 = l > 0.f ? fmaf(P.m[stat_base + i], kLog2e, log2f(l)) : 1.0e30f;  // l == 0: p becomes 0
+          // l == 0 (fully masked row): force p to 0; kRoundLog2 pre-scales p for pack_bf16_trunc
+          nl = l > 0.f ? ptx::kRoundLog2 - fmaf(P.m[stat_base + i], kLog2e, log2f(l)) : -1.0e30f;
           dl = P.delta[stat_base + i];
         }
-        sh->nlse2[st][row] = ptx::kRoundLog2 - lse2;  // probabilities come out pre-scaled for pack_bf16_trunc
-        sh->delta[st][row] = dl;
-        if (MK == FLEXATTN_MASK_DOCUMENT) sh->doc[st][row] = (i < P.seq_q) ? doc[i] : -1;
-        ptx::named_bar_sync(1, 128);
+        sh->nlse2[st][64 * chain + row] = nl;
+        sh->delta[st][64 * chain + row] = dl;
+        if (MK == FLEXATTN_MASK_DOCUMENT) sh->doc[st][64 * chain + row] = (i < P.seq_q) ? doc[i] : -1;
       }
+      ptx::named_bar_sync(1 + chain, 128);
       if (tid == 0) FA_TRACE(8);
       // a failed wait never leaves the loop early: every thread keeps executing the same named barriers
       if (ok) {
-        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_sdp, n & 1));
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_sdp[chain], n & 1));
         if (!ok) fail_at = 10;
       }
       if (!ok) continue;
       if (tid == 0) FA_TRACE(9);
       ptx::tc_fence_after();
+      uint32_t sr[2][32], pr[2][32];
+      ptx::tmem_ld32(lane_base + colS, sr[0]);
+      ptx::tmem_ld32(lane_base + colS + 32, sr[1]);
+      ptx::tmem_ld32(lane_base + colDP, pr[0]);
+      ptx::tmem_ld32(lane_base + colDP + 32, pr[1]);
+      ptx::tmem_wait_ld();
+      ptx::tmem_ld_acquire(sr[0]);
+      ptx::tmem_ld_acquire(sr[1]);
+      ptx::tmem_ld_acquire(pr[0]);
+      ptx::tmem_ld_acquire(pr[1]);
+      if (tid == 0) FA_TRACE(10);
+      uint32_t pk_p[32], pk_ds[32];
       const float abase = slope2 * (float)(j - i0);  // ALiBi bias = slope * (j - i), i = i0 + column
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sr[2][32], pr[2][32];
-        ptx::tmem_ld32(lane_base + kColS + half * 64, sr[0]);
-        ptx::tmem_ld32(lane_base + kColS + half * 64 + 32, sr[1]);
-        ptx::tmem_ld32(lane_base + kColDP + half * 64, pr[0]);
-        ptx::tmem_ld32(lane_base + kColDP + half * 64 + 32, pr[1]);
-        ptx::tmem_wait_ld();
-        ptx::tmem_ld_acquire(sr[0]);
-        ptx::tmem_ld_acquire(sr[1]);
-        ptx::tmem_ld_acquire(pr[0]);
-        ptx::tmem_ld_acquire(pr[1]);
-        if (tid == 0) FA_TRACE(10 + 2 * half);
-        uint32_t pk_p[32], pk_ds[32];
-        // ALiBi bias = slope * (j - i) with i = i0 + half * 64 + column
-        const float abase_h = abase - slope2 * (float)(half * 64);
-        if (partial)
-          dkv_half_math<SK, MK, true>(sr, pr, pk_p, pk_ds, &sh->nlse2[st][half * 64], &sh->delta[st][half * 64],
-                                      &sh->doc[st][half * 64], i0 + half * 64, j, dj, P.seq_q, P.window, P.stride, c2,
-                                      slope2, abase_h, capl2, csc);
-        else
-          dkv_half_math<SK, MK, false>(sr, pr, pk_p, pk_ds, &sh->nlse2[st][half * 64], &sh->delta[st][half * 64],
-                                       &sh->doc[st][half * 64], i0 + half * 64, j, dj, P.seq_q, P.window, P.stride, c2,
-                                       slope2, abase_h, capl2, csc);
-        ptx::tmem_st32(lane_base + kColS + half * 32, pk_p);
-        ptx::tmem_st32(lane_base + kColDP + half * 32, pk_ds);
-        if (tid == 0) FA_TRACE(11 + 2 * half);
-      }
+      if (partial)
+        dkv_half_math<SK, MK, true>(sr, pr, pk_p, pk_ds, &sh->nlse2[st][64 * chain], &sh->delta[st][64 * chain],
+                                    &sh->doc[st][64 * chain], i0, j, dj, P.seq_q, P.window, P.stride, c2, slope2,
+                                    abase, capl2, csc);
+      else
+        dkv_half_math<SK, MK, false>(sr, pr, pk_p, pk_ds, &sh->nlse2[st][64 * chain], &sh->delta[st][64 * chain],
+                                     &sh->doc[st][64 * chain], i0, j, dj, P.seq_q, P.window, P.stride, c2, slope2,
+                                     abase, capl2, csc);
+      ptx::tmem_st32(lane_base + colS, pk_p);
+      ptx::tmem_st32(lane_base + colDP, pk_ds);
+      if (tid == 0) FA_TRACE(11);
       ptx::tmem_wait_st();
       ptx::tc_fence_before();
-      ptx::mbar_arrive(&sh->bar_pds);
-      if (tid == 0) FA_TRACE(14);
+      ptx::mbar_arrive(&sh->bar_pds[chain]);
+      if (tid == 0) FA_TRACE(12);
     }
 
-    if (ok && n_tiles > 0) {
-      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_acc, (n_tiles - 1) & 1));
+    if (ok && N > 0) {
+      // both chains' accumulation MMAs of the last tile must have completed
+      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_acc[0], (N - 1) & 1) &&
+                                       ptx::mbar_wait(&sh->bar_acc[1], (N - 1) & 1));
       if (!ok) fail_at = 12;
     }
     if (ok) {
-      if (n_tiles > 0) ptx::tc_fence_after();
+      if (N > 0) ptx::tc_fence_after();
       const size_t grow = (size_t)bh * P.seq_k + j;
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
+      {
+        const int which = chain;  // warpgroup 0 stores dK, warpgroup 1 stores dV
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(which ? P.dv : P.dk) + grow * D;
         const float sc = which ? 1.f : P.sm_scale;
         const uint32_t col = which ? kColDV : kColDK;
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
           uint32_t r[32];
-          if (n_tiles > 0) {
+          if (N > 0) {
             ptx::tmem_ld32(lane_base + col + c0, r);
             ptx::tmem_wait_ld();
             ptx::tmem_ld_acquire(r);
@@ -326,7 +380,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
   }

@@ -6,24 +6,37 @@
 //
 //   S  = Q K^T, dP = dO V^T         tcgen05.mma, f32 accumulators in tensor memory (128 + 128 columns)
 //   dS = P o (dP - delta) o sigma'  in registers by two warpgroups: threads t and t + 128 own query row t and
-//                                   one 64-column half of the tile each; P is rebuilt from (l, m) as
-//                                   exp2(x2 - (m log2e + log2 l)); written back as packed bf16 over S
-//   dQ += dS K                      tcgen05.mma, A = dS from tensor memory, B = the same K tile read
-//                                   MN-major; dQ (D columns) stays in tensor memory across kv tiles
+//                                   64 key columns each; P is rebuilt from (l, m) as
+//                                   exp2(x2 - (m log2e + log2 l)); dS is written as bf16 to a shared-memory
+//                                   tile in the K-major operand layout
+//   dQ += dS K                      tcgen05.mma, A = dS from shared memory, B = the same K tile read MN-major;
+//                                   dQ (D columns) stays in tensor memory across kv tiles
 //
-// and the epilogue scales by sm_scale and stores bf16.  Masks run only on partial tiles.
+// Because dS does not go back into the S / dP columns, those are free again as soon as the warpgroups have
+// loaded them into registers: the MMAs of tile n+1 run during the element-wise math of tile n.  The epilogue
+// scales by sm_scale and stores bf16.  Masks run only on partial tiles.
 #include "sm100.cuh"
+
+#ifdef FLEXATTN_TRACE
+#define FA_TRACE(slot)                                                          \
+  do {                                                                          \
+    if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64)     \
+      P.trace[n * 16 + (slot)] = clock64();                                     \
+  } while (0)
+#else
+#define FA_TRACE(slot)
+#endif
 
 namespace flexattn {
 namespace {
 
-constexpr int kThreads = 288;   // warps 0-3 and 4-7: element-wise warpgroups; warp 8: TMA + MMA issue
-constexpr int kCtrlWarp = 8;
+constexpr int kThreads = 320;  // warps 0-3, 4-7: element-wise warpgroups (64 key columns each); 8: MMA; 9: TMA
+constexpr int kMmaWarp = 8, kTmaWarp = 9;
 
 struct DqSmem {
-  uint64_t bar_q, bar_kv[2], bar_sdp, bar_ds, bar_dq;
+  uint64_t bar_q, bar_qtm, bar_kv[3], bar_sdp, bar_ld, bar_ds, bar_dq;
   uint32_t tmem_base;
-  int32_t doc[2][kTile];
+  alignas(16) int32_t doc[2][kTile];
 };
 
 // This thread's 64 columns (keys j_first .. j_first+63) of its query row: raw S and dP in, packed bf16 dS out.
@@ -76,35 +89,42 @@ __global__ void __launch_bounds__(kThreads, 1)
                     const DevParams P, int* abort_flag) {
   constexpr int kPanels = D / 64;
   constexpr uint32_t kTileBytes = kPanels * ptx::kPanelBytes;
+  constexpr uint32_t kDsBytes = 2 * ptx::kPanelBytes;  // dS tile: 128 query rows x 128 keys, bf16
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 256;
+  constexpr uint32_t kColQ = 384, kColDO = 384 + D / 2;  // Q and dO as packed bf16 A operands (D/2 columns each)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;
-  uint8_t* sDO = smem + kTileBytes;
-  uint8_t* sK = smem + 2 * kTileBytes;  // two stages
-  uint8_t* sV = smem + 4 * kTileBytes;  // two stages
-  DqSmem* sh = reinterpret_cast<DqSmem*>(smem + 6 * kTileBytes);
+  // K/V ring of three stages (stage s: K at 2s, V at 2s+1 tiles).  Stage 2 first stages Q and dO, which are
+  // copied to tensor memory once and then never read from shared memory again.
+  uint8_t* sKV = smem;
+  uint8_t* sQ = smem + 4 * kTileBytes;
+  uint8_t* sDO = smem + 5 * kTileBytes;
+  uint8_t* sDS = smem + 6 * kTileBytes;
+  DqSmem* sh = reinterpret_cast<DqSmem*>(smem + 6 * kTileBytes + kDsBytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qt = P.n_qt - 1 - (int)blockIdx.x;
   const int bh = blockIdx.y, b = bh / P.heads, h = bh % P.heads;
   const int4 rm = P.row_map[(size_t)(P.map_rows > 1 ? b : 0) * P.n_qt + qt];
-  const int n_tiles = rm.y - rm.x;
+  const int N = rm.y - rm.x;
 
   if (*reinterpret_cast<volatile int*>(abort_flag) != 0) return;
 
   if (tid == 0) {
     ptx::mbar_init(&sh->bar_q, 1);
+    ptx::mbar_init(&sh->bar_qtm, 256);
     ptx::mbar_init(&sh->bar_kv[0], 1);
     ptx::mbar_init(&sh->bar_kv[1], 1);
+    ptx::mbar_init(&sh->bar_kv[2], 1);
     ptx::mbar_init(&sh->bar_sdp, 1);
+    ptx::mbar_init(&sh->bar_ld, 256);
     ptx::mbar_init(&sh->bar_ds, 256);
     ptx::mbar_init(&sh->bar_dq, 1);
     ptx::fence_barrier_init();
   }
-  if (warp == kCtrlWarp) {
+  if (warp == kMmaWarp) {
     ptx::tmem_alloc(&sh->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -113,73 +133,100 @@ __global__ void __launch_bounds__(kThreads, 1)
   ptx::tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
 
-  if (warp == kCtrlWarp) {
-    if (lane == 0 && n_tiles > 0) {
+  if (warp == kTmaWarp) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && N > 0) {
       bool ok = true;
-      int fail_at = 1;
       ptx::prefetch_tensormap(&tm_q);
       ptx::prefetch_tensormap(&tm_do);
       ptx::prefetch_tensormap(&tm_k);
       ptx::prefetch_tensormap(&tm_v);
       ptx::mbar_arrive_expect_tx(&sh->bar_q, 2 * kTileBytes);
-      ptx::mbar_arrive_expect_tx(&sh->bar_kv[0], 2 * kTileBytes);
 #pragma unroll
       for (int p = 0; p < kPanels; ++p) {
         ptx::tma_load_3d(sQ + p * ptx::kPanelBytes, &tm_q, &sh->bar_q, p * 64, qt * kTile, bh);
         ptx::tma_load_3d(sDO + p * ptx::kPanelBytes, &tm_do, &sh->bar_q, p * 64, qt * kTile, bh);
-        ptx::tma_load_3d(sK + p * ptx::kPanelBytes, &tm_k, &sh->bar_kv[0], p * 64, rm.x * kTile, bh);
-        ptx::tma_load_3d(sV + p * ptx::kPanelBytes, &tm_v, &sh->bar_kv[0], p * 64, rm.x * kTile, bh);
       }
+      for (int n = 0; n < N && ok; ++n) {
+        const int st = n % 3;
+        if (n == 2) {  // stage 2 staged Q and dO: wait until they have been copied to tensor memory
+          ok = ptx::mbar_wait(&sh->bar_qtm, 0);
+          if (!ok) break;
+        } else if (n >= 3) {  // the stage held tile n-3, whose last reader is the dQ MMA of that tile
+          ok = ptx::mbar_wait(&sh->bar_dq, (n - 3) & 1);
+          if (!ok) break;
+        }
+        uint8_t* dK = sKV + (2 * st) * kTileBytes;
+        uint8_t* dV = sKV + (2 * st + 1) * kTileBytes;
+        ptx::mbar_arrive_expect_tx(&sh->bar_kv[st], 2 * kTileBytes);
+#pragma unroll
+        for (int p = 0; p < kPanels; ++p) {
+          ptx::tma_load_3d(dK + p * ptx::kPanelBytes, &tm_k, &sh->bar_kv[st], p * 64, (rm.x + n) * kTile, bh);
+          ptx::tma_load_3d(dV + p * ptx::kPanelBytes, &tm_v, &sh->bar_kv[st], p * 64, (rm.x + n) * kTile, bh);
+        }
+      }
+      if (!ok) give_up(abort_flag, P.status, 2, 20);
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer
+    // Q and dO are A operands from tensor memory (the warpgroups copy them there once): an MMA with both
+    // operands in shared memory reads 8 KB per 64 cycles, the whole shared-memory bandwidth of the SM, and this
+    // kernel also streams K, V and dS through shared memory.  S(n+1), dP(n+1) are issued as soon as the warpgroups have READ S(n), dP(n) out of tensor memory (dS goes
+    // back through shared memory, not through the S columns), so the tensor core works on the next tile while
+    // the warpgroups do the element-wise math of this one; dQ += dS(n) K(n) follows when dS(n) is in place.
+    if (lane == 0 && N > 0) {
+      bool ok = true;
+      int fail_at = 1;
       constexpr uint32_t idesc_s = ptx::make_idesc(128, 128, false);
       constexpr uint32_t idesc_dq = ptx::make_idesc(128, D, true);
-      const ptx::DescBase bQ = ptx::base_kmajor(ptx::smem_u32(sQ)), bDO = ptx::base_kmajor(ptx::smem_u32(sDO));
-      ok = ptx::mbar_wait(&sh->bar_q, 0);
-      for (int n = 0; n < n_tiles && ok; ++n) {
-        const int st = n & 1;
-        const ptx::DescBase bK = ptx::base_kmajor(ptx::smem_u32(sK + st * kTileBytes)),
-                            bV = ptx::base_kmajor(ptx::smem_u32(sV + st * kTileBytes)),
-                            bKt = ptx::base_mnmajor(ptx::smem_u32(sK + st * kTileBytes));
-        if (n > 0) {
-          // dQ MMA of the previous tile done: S/dP columns and the other K/V stage are free
-          ok = ptx::mbar_wait(&sh->bar_dq, (n - 1) & 1);
-          if (!ok) { fail_at = 2; break; }
-        }
-        if (n + 1 < n_tiles) {
-          uint8_t* nK = sK + (st ^ 1) * kTileBytes;
-          uint8_t* nV = sV + (st ^ 1) * kTileBytes;
-          ptx::mbar_arrive_expect_tx(&sh->bar_kv[st ^ 1], 2 * kTileBytes);
-#pragma unroll
-          for (int p = 0; p < kPanels; ++p) {
-            ptx::tma_load_3d(nK + p * ptx::kPanelBytes, &tm_k, &sh->bar_kv[st ^ 1], p * 64, (rm.x + n + 1) * kTile, bh);
-            ptx::tma_load_3d(nV + p * ptx::kPanelBytes, &tm_v, &sh->bar_kv[st ^ 1], p * 64, (rm.x + n + 1) * kTile, bh);
-          }
-        }
-        ok = ptx::mbar_wait(&sh->bar_kv[st], (n >> 1) & 1);
-        if (!ok) { fail_at = 3; break; }
-        ptx::tc_fence_after();
+      const ptx::DescBase bDS = ptx::base_kmajor(ptx::smem_u32(sDS));
+      const uint32_t aKV = ptx::smem_u32(sKV);
+      auto issue_sdp = [&](int n) {
+        const uint32_t st_off = (uint32_t)(n % 3) * 2 * kTileBytes;
+        const ptx::DescBase bK = ptx::base_kmajor(aKV + st_off), bV = ptx::base_kmajor(aKV + st_off + kTileBytes);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(tmem + kColS, ptx::desc_at(bQ, ptx::koff_kmajor(kk)), ptx::desc_at(bK, ptx::koff_kmajor(kk)), idesc_s,
-                      kk > 0);
+          ptx::mma_ts(tmem + kColS, tmem + kColQ + kk * 8, ptx::desc_at(bK, ptx::koff_kmajor(kk)), idesc_s, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(tmem + kColDP, ptx::desc_at(bDO, ptx::koff_kmajor(kk)), ptx::desc_at(bV, ptx::koff_kmajor(kk)), idesc_s,
-                      kk > 0);
+          ptx::mma_ts(tmem + kColDP, tmem + kColDO + kk * 8, ptx::desc_at(bV, ptx::koff_kmajor(kk)), idesc_s, kk > 0);
         ptx::mma_commit(&sh->bar_sdp);
-        ok = ptx::mbar_wait(&sh->bar_ds, n & 1);
-        if (!ok) { fail_at = 4; break; }
+      };
+      ok = ptx::mbar_wait(&sh->bar_qtm, 0) && ptx::mbar_wait(&sh->bar_kv[0], 0);  // Q, dO in tensor memory; K, V landed
+      if (ok) {
         ptx::tc_fence_after();
+        issue_sdp(0);
+      }
+      for (int n = 0; n < N && ok; ++n) {
+        const uint32_t par = n & 1;
+        if (n + 1 < N) {
+          ok = ptx::mbar_wait(&sh->bar_ld, par);  // S(n), dP(n) are in registers: their columns are free
+          if (!ok) { fail_at = 2; break; }
+          FA_TRACE(0);
+          ok = ptx::mbar_wait(&sh->bar_kv[(n + 1) % 3], ((n + 1) / 3) & 1);
+          if (!ok) { fail_at = 3; break; }
+          ptx::tc_fence_after();
+          issue_sdp(n + 1);
+          FA_TRACE(1);
+        }
+        ok = ptx::mbar_wait(&sh->bar_ds, par);  // dS(n) written to shared memory
+        if (!ok) { fail_at = 4; break; }
+        FA_TRACE(2);
+        ptx::tc_fence_after();
+        const ptx::DescBase bKt = ptx::base_mnmajor(aKV + (uint32_t)(n % 3) * 2 * kTileBytes);
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
-          ptx::mma_ts(tmem + kColDQ, tmem + kColS + kk * 8, ptx::desc_at(bKt, ptx::koff_mnmajor(kk)), idesc_dq,
-                      (n > 0) || (kk > 0));
+          ptx::mma_ss(tmem + kColDQ, ptx::desc_at(bDS, ptx::koff_kmajor(kk)), ptx::desc_at(bKt, ptx::koff_mnmajor(kk)),
+                      idesc_dq, (n > 0) || (kk > 0));
         ptx::mma_commit(&sh->bar_dq);
+        FA_TRACE(3);
       }
       if (!ok) give_up(abort_flag, P.status, 2, fail_at);
     }
   } else {
-    const int row = tid & 127;         // query row inside the tile = TMEM lane
-    const int half = tid >> 7;         // which 64-column half of every tile this thread handles
+    // ------------------------------------------------------------------ element-wise warpgroups
+    const int row = tid & 127;   // query row inside the tile = TMEM lane
+    const int half = tid >> 7;   // which 64 key columns of every tile this thread handles
     const int i = qt * kTile + row;
     const bool row_ok = i < P.seq_q;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -190,22 +237,61 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
     const int di = (MK == FLEXATTN_MASK_DOCUMENT && row_ok) ? doc[i] : 0;
     const size_t grow = (size_t)bh * P.seq_q + i;
-    float lse2 = 0.f, delta = 0.f;
+    float nlse2 = ptx::kRoundLog2, delta = 0.f;
     if (row_ok) {
       const float l = P.l[grow];
-      lse2 = l > 0.f ? fmaf(P.m[grow], kLog2e, log2f(l)) : 1.0e30f;
+      // l == 0 (fully masked row): force p to 0; kRoundLog2 pre-scales p (and so dS) for pack_bf16_trunc
+      nlse2 = l > 0.f ? ptx::kRoundLog2 - fmaf(P.m[grow], kLog2e, log2f(l)) : -1.0e30f;
       delta = P.delta[grow];
     }
+    // this thread's 128 bytes of the dS tile: row `row` of panel `half`, 16-byte chunk j at slot j ^ (row & 7)
+    uint8_t* ds_row = sDS + half * ptx::kPanelBytes + row * 128;
     bool ok = true;
     int fail_at = 0;
 
-    for (int n = 0; n < n_tiles; ++n) {
-      const int kt = rm.x + n, j0 = kt * kTile;
+    // Q and dO rows -> tensor memory as packed bf16 (element d of row r at lane r, column d / 2).  Thread (row,
+    // half) moves the 64 elements of 128-byte panel `half`: chunk j of the row sits at slot j ^ (row & 7).
+    if (N > 0) {
+      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_q, 0));
+      if (!ok) fail_at = 9;
+      if (ok) {
+        if constexpr (D == 128) {
+#pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            const uint8_t* src = (which ? sDO : sQ) + half * ptx::kPanelBytes + row * 128;
+            uint32_t r[32];
+#pragma unroll
+            for (int jc = 0; jc < 8; ++jc) {
+              const uint4 v4 = *reinterpret_cast<const uint4*>(src + ((jc ^ (row & 7)) << 4));
+              r[4 * jc] = v4.x; r[4 * jc + 1] = v4.y; r[4 * jc + 2] = v4.z; r[4 * jc + 3] = v4.w;
+            }
+            ptx::tmem_st32(lane_base + (which ? kColDO : kColQ) + half * 32, r);
+          }
+        } else {  // D == 64: one panel per tensor; warpgroup 0 moves Q, warpgroup 1 moves dO
+          const uint8_t* src = (half ? sDO : sQ) + row * 128;
+          uint32_t r[32];
+#pragma unroll
+          for (int jc = 0; jc < 8; ++jc) {
+            const uint4 v4 = *reinterpret_cast<const uint4*>(src + ((jc ^ (row & 7)) << 4));
+            r[4 * jc] = v4.x; r[4 * jc + 1] = v4.y; r[4 * jc + 2] = v4.z; r[4 * jc + 3] = v4.w;
+          }
+          ptx::tmem_st32(lane_base + (half ? kColDO : kColQ), r);
+        }
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+      }
+      ptx::mbar_arrive(&sh->bar_qtm);
+    }
+
+    for (int n = 0; n < N; ++n) {
+      const int kt = rm.x + n, j0 = kt * kTile + 64 * half;  // first key position of this thread's columns
       const bool partial = !(kt >= rm.z && kt < rm.w);
       if (MK == FLEXATTN_MASK_DOCUMENT && partial) {
-        const int j = j0 + row;
-        if (half == 0) sh->doc[n & 1][row] = (j < P.seq_k) ? doc[j] : -1;
-        ptx::named_bar_sync(1, 256);
+        if (row < 64) {
+          const int j = j0 + row;
+          sh->doc[n & 1][64 * half + row] = (j < P.seq_k) ? doc[j] : -1;
+        }
+        ptx::named_bar_sync(1 + half, 128);
       }
       // a failed wait never leaves the loop early: every thread keeps executing the same named barriers
       if (ok) {
@@ -213,46 +299,56 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!ok) fail_at = 10;
       }
       if (!ok) continue;
+      if (tid == 0) FA_TRACE(8);
       ptx::tc_fence_after();
-      const float abase = slope2 * (float)(j0 - i);
-      {
-        uint32_t sr[2][32], pr[2][32];
-        ptx::tmem_ld32(lane_base + kColS + half * 64, sr[0]);
-        ptx::tmem_ld32(lane_base + kColS + half * 64 + 32, sr[1]);
-        ptx::tmem_ld32(lane_base + kColDP + half * 64, pr[0]);
-        ptx::tmem_ld32(lane_base + kColDP + half * 64 + 32, pr[1]);
-        ptx::tmem_wait_ld();
-        ptx::tmem_ld_acquire(sr[0]);
-        ptx::tmem_ld_acquire(sr[1]);
-        ptx::tmem_ld_acquire(pr[0]);
-        ptx::tmem_ld_acquire(pr[1]);
-        uint32_t pk[32];
-        const float abase_h = abase + slope2 * (float)(half * 64);
-        if (partial)
-          dq_half_math<SK, MK, true>(sr, pr, pk, ptx::kRoundLog2 - lse2, delta, &sh->doc[n & 1][half * 64], i, di, j0 + half * 64,
-                                     P.seq_k, P.window, P.stride, c2, slope2, abase_h, capl2, csc);
-        else
-          dq_half_math<SK, MK, false>(sr, pr, pk, ptx::kRoundLog2 - lse2, delta, &sh->doc[n & 1][half * 64], i, di, j0 + half * 64,
-                                      P.seq_k, P.window, P.stride, c2, slope2, abase_h, capl2, csc);
-        ptx::tmem_st32(lane_base + kColS + half * 32, pk);
-      }
-      ptx::tmem_wait_st();
+      uint32_t sr[2][32], pr[2][32];
+      ptx::tmem_ld32(lane_base + kColS + half * 64, sr[0]);
+      ptx::tmem_ld32(lane_base + kColS + half * 64 + 32, sr[1]);
+      ptx::tmem_ld32(lane_base + kColDP + half * 64, pr[0]);
+      ptx::tmem_ld32(lane_base + kColDP + half * 64 + 32, pr[1]);
+      ptx::tmem_wait_ld();
+      ptx::tmem_ld_acquire(sr[0]);
+      ptx::tmem_ld_acquire(sr[1]);
+      ptx::tmem_ld_acquire(pr[0]);
+      ptx::tmem_ld_acquire(pr[1]);
       ptx::tc_fence_before();
+      ptx::mbar_arrive(&sh->bar_ld);  // S / dP columns may be overwritten by the next tile's MMAs
+      if (tid == 0) FA_TRACE(9);
+      uint32_t pk[32];
+      const float abase = slope2 * (float)(j0 - i);
+      if (partial)
+        dq_half_math<SK, MK, true>(sr, pr, pk, nlse2, delta, &sh->doc[n & 1][64 * half], i, di, j0, P.seq_k, P.window,
+                                   P.stride, c2, slope2, abase, capl2, csc);
+      else
+        dq_half_math<SK, MK, false>(sr, pr, pk, nlse2, delta, &sh->doc[n & 1][64 * half], i, di, j0, P.seq_k, P.window,
+                                    P.stride, c2, slope2, abase, capl2, csc);
+      if (tid == 0) FA_TRACE(10);
+      if (n > 0) {  // the dQ MMA of the previous tile must have read the dS buffer
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dq, (n - 1) & 1));
+        if (!ok) { fail_at = 11; continue; }
+      }
+#pragma unroll
+      for (int jc = 0; jc < 8; ++jc) {
+        const uint4 v4 = make_uint4(pk[4 * jc], pk[4 * jc + 1], pk[4 * jc + 2], pk[4 * jc + 3]);
+        *reinterpret_cast<uint4*>(ds_row + ((jc ^ (row & 7)) << 4)) = v4;
+      }
+      ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the MMA's shared-memory reads
       ptx::mbar_arrive(&sh->bar_ds);
+      if (tid == 0) FA_TRACE(11);
     }
 
-    if (ok && n_tiles > 0) {
-      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dq, (n_tiles - 1) & 1));
+    if (ok && N > 0) {
+      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dq, (N - 1) & 1));
       if (!ok) fail_at = 12;
     }
     if (ok) {
-      if (n_tiles > 0) ptx::tc_fence_after();
+      if (N > 0) ptx::tc_fence_after();
       __nv_bfloat16* out = static_cast<__nv_bfloat16*>(P.dq) + grow * D;
       const float sc = P.sm_scale;
 #pragma unroll 1
       for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
         uint32_t r[32];
-        if (n_tiles > 0) {
+        if (N > 0) {
           ptx::tmem_ld32(lane_base + kColDQ + c0, r);
           ptx::tmem_wait_ld();
           ptx::tmem_ld_acquire(r);
@@ -279,7 +375,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == kCtrlWarp) {
+  if (warp == kMmaWarp) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
   }
@@ -288,7 +384,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 template <int D, int SK, int MK>
 int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const CUtensorMap& tdo,
                const CUtensorMap& tk, const CUtensorMap& tv, int* abort_flag) {
-  constexpr size_t smem = 6 * (D / 64) * ptx::kPanelBytes + sizeof(DqSmem) + 1024;
+  constexpr size_t smem = 6 * (D / 64) * ptx::kPanelBytes + 2 * ptx::kPanelBytes + sizeof(DqSmem) + 1024;
   // 512 TMEM columns per CTA: never let two CTAs share an SM (the second would spin in tcgen05.alloc)
   constexpr size_t smem_req = smem > 120 * 1024 ? smem : 120 * 1024;
   auto kern = dq_sm100_kernel<D, SK, MK>;

@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (ok) {
         float ls[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[32];
-        const float nm = ptx::kRoundLog2 - m_ref;  // pre-scaled by (1 + 2^-9) for pack_bf16_trunc; cancels in o = acc / l
+        const float nm = ptx::kRoundLog2 - m_ref;  // pre-scaled by (1 + 2^-9) for pack_bf16_trunc; compensates the truncation
 #pragma unroll
         for (int c = 0; c < kHalf; c += 2) {
           const float p0 = ptx::ex2(fmaf(x[c], xs, nm)), p1 = ptx::ex2(fmaf(x[c + 1], xs, nm));
@@ -378,7 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::named_bar_sync(1, 256);
     l = sh->lsum[0][row] + sh->lsum[1][row];
     if (ok) {
-      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      const float inv_l = l > 0.f ? ptx::kRoundUp / l : 0.f;  // l sums the pre-scaled probabilities
       const size_t grow = (size_t)bh * P.seq_q + i;
       if (N > 0) ptx::tc_fence_after();
       __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(P.o) + grow * D;

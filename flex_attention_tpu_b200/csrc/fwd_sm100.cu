@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
         uint32_t pk[32];
 #pragma unroll
         for (int c = 0; c < 64; c += 2) {
-          // pre-scaled by (1 + 2^-9) for pack_bf16_trunc; the factor cancels in o = acc / l
+          // pre-scaled by (1 + 2^-9) for pack_bf16_trunc; the factor compensates the truncation
           const float p0 = ptx::ex2(fmaf(x[c0 + c], xs, nm)), p1 = ptx::ex2(fmaf(x[c0 + c + 1], xs, nm));
           ls[(c >> 1) & 3] += p0 + p1;
           pk[c >> 1] = ptx::pack_bf16_trunc(p0, p1);
@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
       if (!ok) fail_at = 12;
     }
     if (ok) {
-      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      const float inv_l = l > 0.f ? ptx::kRoundUp / l : 0.f;  // l sums the pre-scaled probabilities
       const size_t grow = (size_t)bh * P.seq_q + i;
       if (n_tiles > 0) ptx::tc_fence_after();
       __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(P.o) + grow * D;

@@ -210,6 +210,39 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major,
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Warp-uniform issue helpers.  The MMA / TMA warps run their control loops with all 32 lanes converged and
+// predicate only the asynchronous instruction itself on `issue` (true in one lane): descriptor and address
+// arithmetic then stays warp-uniform, which lets the compiler keep it on the uniform datapath instead of
+// converting vector registers for every tcgen05.mma (a single diverged lane issues an MMA only every
+// 55-75 cycles, less than the 64 cycles of tensor work a 128x128x16 MMA carries).
+__device__ __forceinline__ void mma_ss_if(uint32_t issue, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(issue)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_if(uint32_t issue, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(issue)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_if(uint32_t issue, uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n" ::"r"(smem_u32(bar)),
+      "r"(issue)
+      : "memory");
+}
+// all 32 lanes wait; the result is made warp-uniform
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+}
+
 // D[tmem] (+)= A[smem] * B[smem]      (issued by ONE thread)
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                        uint32_t accumulate) {
@@ -245,9 +278,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // integer pipe) of values that were pre-multiplied by (1 + 2^-9): adding between a quarter and half a bf16
 // ulp before dropping the low mantissa bits is rounding to nearest up to a bias of about -2^-11.  The
 // pre-multiplication is free: probabilities get it by adding kRoundLog2 = log2(1 + 2^-9) to the exp2
-// argument, products of such a probability inherit it.
+// argument, products of such a probability inherit it.  The PACKED value then approximates the original
+// number (the factor only compensates the truncation); an f32 sum of the pre-scaled values, such as the
+// softmax denominator, still carries the factor kRoundUp and must be divided by it.
 constexpr float kRoundLog2 = 0.0028150156f;
-constexpr float kRoundInv = 1.0f / 1.001953125f;
+constexpr float kRoundUp = 1.001953125f;
+constexpr float kRoundInv = 1.0f / kRoundUp;
 __device__ __forceinline__ uint32_t pack_bf16_trunc(float lo, float hi) {
   return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
 }
