@@ -292,21 +292,6 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// exp2 on the FMA pipe (no special-function unit): floor/fraction split with the 1.5*2^23 trick, a cubic
-// for 2^f on [0,1) (max relative error 8.6e-5, below the 2^-9 rounding of a bf16 probability) and the
-// integer part added straight into the exponent field.  Valid for x <= 100; anything below -125 returns
-// about 2^-125 (used for masked logits, which must come out as "almost zero", never NaN).  Mixing this
-// with ex2.approx element by element relieves the special-function unit, which is the tighter limit of
-// the softmax (16 results per clock per SM against 128 FMA lanes).
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -125.0f);
-  const float t = __fadd_rd(x, 12582912.0f);        // low mantissa bits now hold floor(x)
-  const float f = x - (t - 12582912.0f);            // fractional part in [0, 1)
-  float p = fmaf(f, 0.07706704f, 0.22764499f);
-  p = fmaf(p, f, 0.69511679f);
-  p = fmaf(p, f, 1.0f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
