@@ -1,0 +1,92 @@
+"""Forward + backward of the hot path for inputs that live in HOST memory.
+
+The entry points of this package take device tensors, like the reference's take device arrays.  A caller
+whose q, k, v, dO sit in (pinned) host memory pays for the PCIe transfers; done naively - copy everything
+in, compute, copy everything out - the three phases run one after the other.  ``fwd_bwd_from_host`` splits
+the batch into chunks and runs them through three CUDA streams (host-to-device, compute, device-to-host)
+so that the copies of one chunk overlap the kernels of another and the two copy directions overlap each
+other.  Every (batch, head) slice is independent, so chunking along the batch changes no result.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from .flex_attention_dkv_kernel import flash_attention_bwd_dkv
+from .flex_attention_dq_bwd import bwd_preprocess, flex_attention_bwd_dq
+from .flex_attention_kernel import _flex_attention_impl
+
+
+_STREAMS = {}
+
+
+def _streams(device):
+    """Three long-lived side streams per device (copy in, compute, copy out).  They are reused across calls so
+    that the caching allocator can recycle the per-stream buffers instead of allocating (and synchronising)
+    on every call."""
+    key = (device.type, device.index)
+    if key not in _STREAMS:
+        _STREAMS[key] = tuple(torch.cuda.Stream(device) for _ in range(3))
+    return _STREAMS[key]
+
+
+def fwd_bwd_from_host(q, k, v, do, *, sm_scale, mask_fn=None, block_mask_fn=None, score_fn=None, causal=False,
+                      segment_ids=None, out: Optional[Sequence[torch.Tensor]] = None, chunk_batch: int = 1,
+                      device: Optional[torch.device] = None, backend="auto"):
+    """q, k, v, do: pinned host tensors [B, H, S, D].  Returns host tensors (o, dq, dk, dv) (``out`` if given:
+    four pinned tensors that are overwritten).  ``segment_ids`` ([B, S], host or device) selects the document
+    mask as in the entry points.  The call returns after everything has arrived in host memory."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    B = q.shape[0]
+    if out is None:
+        out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, q, k, v)]
+    o_h, dq_h, dk_h, dv_h = out
+    seg_dev = None
+    if segment_ids is not None:
+        seg_dev = torch.as_tensor(segment_ids).to(device=device, dtype=torch.int32)
+    cur = torch.cuda.current_stream(device)
+    s_in, s_comp, s_out = _streams(device)
+    for s in (s_in, s_comp, s_out):
+        s.wait_stream(cur)
+    slots = 2
+    ev_comp_done = [None] * slots     # compute of the chunk that last used input slot i
+    dev_in = [None] * slots
+    keep = []
+    for ci, b0 in enumerate(range(0, B, chunk_batch)):
+        b1 = min(B, b0 + chunk_batch)
+        slot = ci % slots
+        with torch.cuda.stream(s_in):
+            if ev_comp_done[slot] is not None:
+                s_in.wait_event(ev_comp_done[slot])          # the kernels that read this slot have finished
+            if dev_in[slot] is None or dev_in[slot][0].shape[0] != b1 - b0:
+                dev_in[slot] = [torch.empty((b1 - b0, *t.shape[1:]), dtype=t.dtype, device=device) for t in (q, k, v, do)]
+            for d, h_ in zip(dev_in[slot], (q, k, v, do)):
+                d.copy_(h_[b0:b1], non_blocking=True)
+            ev_in = torch.cuda.Event()
+            ev_in.record(s_in)
+        with torch.cuda.stream(s_comp):
+            s_comp.wait_event(ev_in)
+            qd, kd, vd, dod = dev_in[slot]
+            seg = None if seg_dev is None else seg_dev[b0:b1].contiguous()
+            o, l, m = _flex_attention_impl(qd, kd, vd, None, seg, True, causal, sm_scale, 1, 128, 128, 128, False,
+                                           block_mask_fn, mask_fn, score_fn, backend=backend)
+            delta = bwd_preprocess(o, dod)
+            dq = flex_attention_bwd_dq(qd, kd, vd, None, seg, l, m, o, dod, delta, sm_scale=sm_scale, score_fn=score_fn,
+                                       mask_fn=mask_fn, block_mask_fn=block_mask_fn, causal=causal, backend=backend)
+            dk, dv = flash_attention_bwd_dkv(kd, vd, qd, None, seg, l, m, delta, dod, sm_scale=sm_scale, causal=causal,
+                                             score_fn=score_fn, mask_fn=mask_fn, block_mask_fn=block_mask_fn,
+                                             backend=backend)
+            ev_comp = torch.cuda.Event()
+            ev_comp.record(s_comp)
+            ev_comp_done[slot] = ev_comp
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_comp)
+            for h_, r in zip((o_h, dq_h, dk_h, dv_h), (o, dq, dk, dv)):
+                r.record_stream(s_out)
+                h_[b0:b1].copy_(r, non_blocking=True)
+        keep.append((o, l, m, delta, dq, dk, dv, seg))
+    for s in (s_in, s_comp, s_out):
+        cur.wait_stream(s)
+    cur.synchronize()
+    return o_h, dq_h, dk_h, dv_h
