@@ -152,7 +152,7 @@ int flexattn_fwd(void* stream, const FlexAttnParams* p) {
     // has enough kv tiles to amortise its longer prologue; FLEXATTN_FWD_VARIANT=1|2 forces one (tests).
     int variant = 0;
     if (const char* env = getenv("FLEXATTN_FWD_VARIANT")) variant = atoi(env);
-    if (variant != 1 && variant != 2) variant = p->seq_k >= kPipeMinSeqK ? 2 : 1;
+    if (variant < 1 || variant > 2) variant = p->seq_k >= kPipeMinSeqK ? 2 : 1;
     return variant == 2 ? launch_sm100_fwd_pipe(st, d, p->score_kind, p->mask_kind)
                         : launch_sm100_fwd(st, d, p->score_kind, p->mask_kind);
   }

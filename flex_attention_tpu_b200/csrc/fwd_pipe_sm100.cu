@@ -41,6 +41,7 @@ constexpr int kMmaWarp = 8, kTmaWarp = 9;
 constexpr int kHalf = kTile / 2;
 constexpr int kSBufs = 3;
 constexpr float kLazyRescale = 8.0f;  // log2 units
+constexpr bool kInOrderMma = true;     // rely on issue-order execution of one thread's tcgen05.mma stream
 
 struct PipeSmem {
   uint64_t bar_q, bar_k[2], bar_v[2], bar_kfree[2], bar_s[kSBufs], bar_p[kSBufs], bar_pv[2];
@@ -226,9 +227,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::mma_commit(&sh->bar_pv[n & 1]);
         FA_TRACE(2);
         if (n + kSBufs < N) {
-          // P V of tile n must have consumed P[n] before Q K^T of tile n+3 overwrites the same columns
-          ok = ptx::mbar_wait(&sh->bar_pv[n & 1], (n >> 1) & 1);
-          if (!ok) { fail_at = 5; break; }
+          // Q K^T of tile n+3 overwrites the columns P V of tile n reads its A operand from.  MMAs issued by one
+          // thread execute in issue order, so no wait for P V to complete is needed between the two.
+          if (!kInOrderMma) {
+            ok = ptx::mbar_wait(&sh->bar_pv[n & 1], (n >> 1) & 1);
+            if (!ok) { fail_at = 5; break; }
+          }
           FA_TRACE(3);
           ok = ptx::mbar_wait(&sh->bar_k[(n + kSBufs) & 1], ((n + kSBufs) >> 1) & 1);
           if (!ok) { fail_at = 6; break; }
