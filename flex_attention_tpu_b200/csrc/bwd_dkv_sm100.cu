@@ -33,6 +33,7 @@ namespace {
 
 constexpr int kThreads = 320;  // warps 0-3, 4-7: element-wise warpgroups (one per half-tile chain); 8: MMA; 9: TMA
 constexpr int kMmaWarp = 8, kTmaWarp = 9;
+constexpr bool kInOrderMma = true;  // rely on issue-order execution of one thread's tcgen05.mma stream
 
 struct DkvSmem {
   uint64_t bar_kv, bar_q[2], bar_free[2], bar_sdp[2], bar_pds[2], bar_acc[2], bar_zero;
@@ -236,9 +237,12 @@ __global__ void __launch_bounds__(kThreads, 1)
               ok = ptx::mbar_wait(&sh->bar_q[(n + 1) & 1], ((n + 1) >> 1) & 1);
               if (!ok) { fail_at = 4; break; }
             }
-            // chain c's accumulation MMAs must have consumed P^T_c / dS^T_c before the next S^T_c / dP^T_c land
-            ok = ptx::mbar_wait(&sh->bar_acc[c], par);
-            if (!ok) { fail_at = 5 + c; break; }
+            // chain c's accumulation MMAs read P^T_c / dS^T_c from the columns the next S^T_c / dP^T_c overwrite.
+            // MMAs issued by one thread execute in issue order, so no wait for their completion is needed.
+            if (!kInOrderMma) {
+              ok = ptx::mbar_wait(&sh->bar_acc[c], par);
+              if (!ok) { fail_at = 5 + c; break; }
+            }
             ptx::tc_fence_after();
             issue_sdp(n + 1, c);
             if (c == 0) FA_TRACE(2); else FA_TRACE(5);

@@ -93,7 +93,7 @@ def test_simt_bfloat16(mask_kind, score_kind):
 def test_tensor_core_bfloat16(mask_kind, score_kind, D, fwd_variant, monkeypatch):
     """The tcgen05 kernels: every mask x score functor, both head dims, ragged sequence (not a tile multiple),
     and both forward kernels (1 = one score tile in flight, 2 = pipelined; chosen by sequence length in
-    normal use, forced here; 3 = two softmax streams)."""
+    normal use, forced here)."""
     monkeypatch.setenv("FLEXATTN_FWD_VARIANT", str(fwd_variant))
     _case(mask_kind, score_kind, torch.bfloat16, 2, 2, 777, 777, D, 105 + D, "tcgen05")
 
