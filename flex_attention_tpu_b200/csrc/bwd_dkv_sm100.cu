@@ -2,9 +2,9 @@
 //
 // Replaces the reference's Pallas dK/dV kernel (flex_attention_dkv_kernel.py:177-280 and its mask-aware
 // twin flash_attention_dkv_bwd.py:183-308).  One CTA owns one 128-row kv tile of one (batch, head): K and
-// V stay in shared memory, Q/dO tiles (and their row statistics) stream through a two-stage ring, and
-// per q tile the TRANSPOSED score tile is formed so that the probabilities land in tensor memory in
-// the layout the next MMA wants as its A operand:
+// V stay in shared memory, Q and dO tiles stream through two-stage rings, and per q tile the TRANSPOSED
+// score tile is formed so that the probabilities land in tensor memory in the layout the next MMA wants as
+// its A operand:
 //
 //   S^T  = K Q^T, dP^T = V dO^T      tcgen05.mma, f32 accumulators (128 + 128 TMEM columns)
 //   P^T, dS^T                        in registers; thread = key row, columns = query positions, whose statistics
@@ -12,10 +12,15 @@
 //                                    packed bf16 over S^T / dP^T
 //   dV += P^T dO ; dK += dS^T Q      tcgen05.mma, A from tensor memory, B = the dO / Q tile read MN-major
 //
-// Every tile is processed as two independent half-tile chains (query columns 0..63 and 64..127), each with
-// its own warpgroup and barriers: while one chain's warpgroup does its element-wise work the tensor core
-// runs the other chain's MMAs, so neither side idles.  dK, dV (D columns each) stay in tensor memory
-// across q tiles: 512 columns in total, one CTA per SM.
+// The four MMA groups of consecutive tiles are interleaved on the tensor core so that each element-wise phase
+// has two other groups to hide behind:
+//
+//   ... dV(n)  S^T(n+1)  dK(n)  dP^T(n+1)  dV(n+1)  S^T(n+2)  dK(n+1) ...
+//
+// P^T(n+1) (the exponentials) is computed while dK(n) and dP^T(n+1) run, dS^T(n+1) while dV(n+1) and S^T(n+2)
+// run.  S^T(n+1) overwrites the columns dV(n) reads P^T(n) from, and dP^T(n+1) those dK(n) reads dS^T(n) from:
+// MMAs issued by one thread execute in issue order, so issuing them in this order is all the protection needed.
+// dK, dV (D columns each) stay in tensor memory across q tiles: 512 columns in total, one CTA per SM.
 #include "sm100.cuh"
 
 #ifdef FLEXATTN_TRACE
@@ -24,56 +29,68 @@
     if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64)     \
       P.trace[n * 16 + (slot)] = clock64();                                     \
   } while (0)
+#define FA_TRACE_AT(idx, slot)                                                           \
+  do {                                                                                   \
+    if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (idx) >= 0 && (idx) < 64) \
+      P.trace[(idx) * 16 + (slot)] = clock64();                                          \
+  } while (0)
 #else
 #define FA_TRACE(slot)
+#define FA_TRACE_AT(idx, slot)
 #endif
 
 namespace flexattn {
 namespace {
 
-constexpr int kThreads = 320;  // warps 0-3, 4-7: element-wise warpgroups (one per half-tile chain); 8: MMA; 9: TMA
+constexpr int kThreads = 320;  // warps 0-3, 4-7: element-wise warpgroups (64 query columns each); 8: MMA; 9: TMA
 constexpr int kMmaWarp = 8, kTmaWarp = 9;
-constexpr bool kInOrderMma = true;  // rely on issue-order execution of one thread's tcgen05.mma stream
 
 struct DkvSmem {
-  uint64_t bar_kv, bar_q[2], bar_free[2], bar_sdp[2], bar_pds[2], bar_acc[2], bar_zero;
+  uint64_t bar_kv, bar_q[2], bar_do[2], bar_qfree[2], bar_dofree[2], bar_s, bar_dp, bar_p, bar_ds, bar_acc, bar_zero;
   uint32_t tmem_base;
   alignas(16) float nlse2[2][kTile];  // -(m log2e + log2 l) of the query rows of the tile in flight
   alignas(16) float delta[2][kTile];
   alignas(16) int32_t doc[2][kTile];
 };
 
-// One 64-column half of a transposed tile: this thread's key row against query columns i_first .. i_first+63.
-// sr / pr: raw S^T and dP^T values; outputs packed bf16 P^T and dS^T.  Query statistics come from shared memory
-// four at a time.  The mask functor is compiled in only for partial tiles.
+// Query statistics are read from shared memory 32 columns at a time INTO REGISTERS before they are needed: the
+// S^T / dP^T MMAs take both operands from shared memory and saturate its bandwidth, so a shared-memory load
+// issued in the middle of the element-wise loop waits a long time.
+__device__ __forceinline__ void load_stats32(float (&dst)[32], const float* __restrict__ src) {
+#pragma unroll
+  for (int c = 0; c < 32; c += 4) {
+    const float4 t = *reinterpret_cast<const float4*>(src + c);
+    dst[c] = t.x;
+    dst[c + 1] = t.y;
+    dst[c + 2] = t.z;
+    dst[c + 3] = t.w;
+  }
+}
+
+// First element-wise phase, 32 columns: this thread's key row against query columns i_first .. i_first+31.
+// s: raw S^T values in, p * dsigma (the factor dS^T needs) out; pk_p: packed bf16 P^T.  The mask functor is
+// compiled in only for partial tiles.
 template <int SK, int MK, bool kPartial>
-__device__ __forceinline__ void dkv_half_math(const uint32_t (&sr)[2][32], const uint32_t (&pr)[2][32],
-                                              uint32_t (&pk_p)[32], uint32_t (&pk_ds)[32],
-                                              const float* __restrict__ s_nlse2, const float* __restrict__ s_delta,
-                                              const int32_t* __restrict__ s_doc, int i_first, int j, int dj, int seq_q,
-                                              int window, int stride, float c2, float slope2, float abase, float capl2,
-                                              float csc) {
+__device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __restrict__ pk_p, const float (&nl)[32],
+                                             const int32_t* __restrict__ s_doc, int i_first, int j, int dj, int seq_q,
+                                             int window, int stride, float c2, float slope2, float abase, float capl2,
+                                             float csc) {
 #pragma unroll
-  for (int c = 0; c < 64; c += 4) {
-    const float4 nl4 = *reinterpret_cast<const float4*>(s_nlse2 + c);
-    const float4 dl4 = *reinterpret_cast<const float4*>(s_delta + c);
-    const float nl[4] = {nl4.x, nl4.y, nl4.z, nl4.w};
-    const float dl[4] = {dl4.x, dl4.y, dl4.z, dl4.w};
-    float pv[4], dv[4];
+  for (int c = 0; c < 32; c += 2) {
+    float pv[2];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 2; ++u) {
       const int cc = c + u;
-      const float s = __uint_as_float(sr[cc >> 5][cc & 31]);
-      const float dp = __uint_as_float(pr[cc >> 5][cc & 31]);
+      const float sv = __uint_as_float(s[cc]);
       float arg, dsig = 1.f;  // arg = log2-domain logit minus the row's log-sum-exp
       if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
-        arg = fmaf(s, c2, fmaf(-slope2, (float)cc, abase) + nl[u]);
+        arg = fmaf(sv, c2, fmaf(-slope2, (float)cc, abase) + nl[cc]);
       } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
-        const float th = ptx::tanh_approx(s * csc);
-        arg = fmaf(capl2, th, nl[u]);
+        const float th = ptx::tanh_approx(sv * csc);
+        arg = fmaf(capl2, th, nl[cc]);
         dsig = fmaf(-th, th, 1.f);
       } else {
-        arg = fmaf(s, c2, nl[u]);
+        arg = fmaf(sv, c2, nl[cc]);
       }
       float p = ptx::ex2(arg);
       if constexpr (kPartial) {
@@ -82,15 +99,22 @@ __device__ __forceinline__ void dkv_half_math(const uint32_t (&sr)[2][32], const
         const bool keep = (i < seq_q) && mask_keep<MK>(i, j, window, stride, di, dj);
         p = keep ? p : 0.f;
       }
-      float d = p * (dp - dl[u]);
-      if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) d *= dsig;
       pv[u] = p;
-      dv[u] = d;
+      if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) p *= dsig;
+      s[cc] = __float_as_uint(p);
     }
     pk_p[c >> 1] = ptx::pack_bf16_trunc(pv[0], pv[1]);
-    pk_p[(c >> 1) + 1] = ptx::pack_bf16_trunc(pv[2], pv[3]);
-    pk_ds[c >> 1] = ptx::pack_bf16_trunc(dv[0], dv[1]);
-    pk_ds[(c >> 1) + 1] = ptx::pack_bf16_trunc(dv[2], dv[3]);
+  }
+}
+
+// Second phase, 32 columns: dS^T = (p dsigma) * (dP^T - delta), packed bf16.
+__device__ __forceinline__ void dkv_ds_math32(const uint32_t (&pd)[32], const uint32_t (&pr)[32],
+                                              uint32_t* __restrict__ pk_ds, const float (&dl)[32]) {
+#pragma unroll
+  for (int c = 0; c < 32; c += 2) {
+    const float d0 = __uint_as_float(pd[c]) * (__uint_as_float(pr[c]) - dl[c]);
+    const float d1 = __uint_as_float(pd[c + 1]) * (__uint_as_float(pr[c + 1]) - dl[c + 1]);
+    pk_ds[c >> 1] = ptx::pack_bf16_trunc(d0, d1);
   }
 }
 
@@ -103,7 +127,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   constexpr uint32_t kTileBytes = kPanels * ptx::kPanelBytes;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 384;
-  constexpr uint32_t kRowsHalfBytes = 64 * 128;  // 64 rows of a K-major panel
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -123,13 +146,17 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (tid == 0) {
     ptx::mbar_init(&sh->bar_kv, 1);
-    ptx::mbar_init(&sh->bar_zero, 256);
+    ptx::mbar_init(&sh->bar_zero, 8);
+    ptx::mbar_init(&sh->bar_s, 1);
+    ptx::mbar_init(&sh->bar_dp, 1);
+    ptx::mbar_init(&sh->bar_p, 8);    // one arrival per warp of the two warpgroups
+    ptx::mbar_init(&sh->bar_ds, 8);
+    ptx::mbar_init(&sh->bar_acc, 1);
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(&sh->bar_q[s], 1);
-      ptx::mbar_init(&sh->bar_free[s], 1);
-      ptx::mbar_init(&sh->bar_sdp[s], 1);
-      ptx::mbar_init(&sh->bar_pds[s], 128);
-      ptx::mbar_init(&sh->bar_acc[s], 1);
+      ptx::mbar_init(&sh->bar_do[s], 1);
+      ptx::mbar_init(&sh->bar_qfree[s], 1);
+      ptx::mbar_init(&sh->bar_dofree[s], 1);
     }
     ptx::fence_barrier_init();
   }
@@ -144,128 +171,149 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
+    // Q and dO have rings of their own: the Q stage of tile n is free once dK(n) has run, the dO stage once
+    // dV(n) has, and each is refilled (tile n+2) as soon as that happens.
     if (lane == 0 && N > 0) {
       bool ok = true;
       ptx::prefetch_tensormap(&tm_q);
       ptx::prefetch_tensormap(&tm_do);
       ptx::prefetch_tensormap(&tm_k);
       ptx::prefetch_tensormap(&tm_v);
+      auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row0) {
+        ptx::mbar_arrive_expect_tx(bar, kTileBytes);
+#pragma unroll
+        for (int p = 0; p < kPanels; ++p) ptx::tma_load_3d(dst + p * ptx::kPanelBytes, tm, bar, p * 64, row0, bh);
+      };
+      // order of first use: K, Q(0), V, dO(0)
       ptx::mbar_arrive_expect_tx(&sh->bar_kv, 2 * kTileBytes);
 #pragma unroll
-      for (int p = 0; p < kPanels; ++p) {
-        ptx::tma_load_3d(sK + p * ptx::kPanelBytes, &tm_k, &sh->bar_kv, p * 64, kt * kTile, bh);
-        ptx::tma_load_3d(sV + p * ptx::kPanelBytes, &tm_v, &sh->bar_kv, p * 64, kt * kTile, bh);
-      }
-      for (int n = 0; n < N && ok; ++n) {
-        const int st = n & 1;
-        if (n >= 2) {  // the stage held tile n-2: wait until all of its MMAs have completed
-          ok = ptx::mbar_wait(&sh->bar_free[st], ((n - 2) >> 1) & 1);
-          if (!ok) break;
-        }
-        ptx::mbar_arrive_expect_tx(&sh->bar_q[st], 2 * kTileBytes);
+      for (int p = 0; p < kPanels; ++p) ptx::tma_load_3d(sK + p * ptx::kPanelBytes, &tm_k, &sh->bar_kv, p * 64, kt * kTile, bh);
+      load_tile(sQ, &tm_q, &sh->bar_q[0], cm.x * kTile);
 #pragma unroll
-        for (int p = 0; p < kPanels; ++p) {
-          ptx::tma_load_3d(sQ + st * kTileBytes + p * ptx::kPanelBytes, &tm_q, &sh->bar_q[st], p * 64,
-                           (cm.x + n) * kTile, bh);
-          ptx::tma_load_3d(sDO + st * kTileBytes + p * ptx::kPanelBytes, &tm_do, &sh->bar_q[st], p * 64,
-                           (cm.x + n) * kTile, bh);
-        }
+      for (int p = 0; p < kPanels; ++p) ptx::tma_load_3d(sV + p * ptx::kPanelBytes, &tm_v, &sh->bar_kv, p * 64, kt * kTile, bh);
+      load_tile(sDO, &tm_do, &sh->bar_do[0], cm.x * kTile);
+      if (N > 1) {
+        load_tile(sQ + kTileBytes, &tm_q, &sh->bar_q[1], (cm.x + 1) * kTile);
+        load_tile(sDO + kTileBytes, &tm_do, &sh->bar_do[1], (cm.x + 1) * kTile);
+      }
+      for (int n = 2; n < N && ok; ++n) {
+        const int st = n & 1;
+        const uint32_t par = ((n - 2) >> 1) & 1;
+        // dV(n-2) is issued before dK(n-2): the dO stage frees first
+        ok = ptx::mbar_wait_relaxed(&sh->bar_dofree[st], par);
+        if (!ok) break;
+        FA_TRACE_AT(n - 2, 6);
+        load_tile(sDO + st * kTileBytes, &tm_do, &sh->bar_do[st], (cm.x + n) * kTile);
+        ok = ptx::mbar_wait_relaxed(&sh->bar_qfree[st], par);
+        if (!ok) break;
+        FA_TRACE_AT(n - 2, 7);
+        load_tile(sQ + st * kTileBytes, &tm_q, &sh->bar_q[st], (cm.x + n) * kTile);
       }
       if (!ok) give_up(abort_flag, P.status, 3, 20);
     }
   } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------------ MMA issuer: two half-tile chains
-    // Chain c owns query columns [64c, 64c+64) of every tile: S^T_c / dP^T_c (N = 64) -> warpgroup c ->
-    // dV, dK += (P^T_c, dS^T_c) x (dO, Q rows 64c..).  The chains alternate on the tensor core so that one
-    // chain's MMAs run while the other chain's warpgroup does its element-wise work.  dK / dV are zeroed by the
-    // warpgroups first, so every accumulation MMA adds.  (N = 64 MMAs cost as many cycles as N = 128 ones - the
-    // A operand fetch of 128 rows bounds them - so the chains buy overlap at the price of tensor efficiency.)
+    // ------------------------------------------------------------------ MMA issuer
+    // dK / dV are zeroed by the warpgroups first, so every accumulation MMA adds.
     if (lane == 0 && N > 0) {
       bool ok = true;
       int fail_at = 1;
-      constexpr uint32_t idesc_s = ptx::make_idesc(128, 64, false);
+      constexpr uint32_t idesc_s = ptx::make_idesc(128, 128, false);
       constexpr uint32_t idesc_acc = ptx::make_idesc(128, D, true);
-      const uint32_t aK = ptx::smem_u32(sK), aV = ptx::smem_u32(sV), aQ = ptx::smem_u32(sQ), aDO = ptx::smem_u32(sDO);
-      const ptx::DescBase bK = ptx::base_kmajor(aK), bV = ptx::base_kmajor(aV);
-      auto issue_sdp = [&](int n, int c) {  // S^T_c = K Q_c^T and dP^T_c = V dO_c^T for tile n
-        const uint32_t off = (uint32_t)(n & 1) * kTileBytes + (uint32_t)c * kRowsHalfBytes;
-        const ptx::DescBase bQ = ptx::base_kmajor(aQ + off), bDO = ptx::base_kmajor(aDO + off);
+      const uint32_t aQ = ptx::smem_u32(sQ), aDO = ptx::smem_u32(sDO);
+      const ptx::DescBase bK = ptx::base_kmajor(ptx::smem_u32(sK)), bV = ptx::base_kmajor(ptx::smem_u32(sV));
+      auto issue_s = [&](int n) {  // S^T = K Q^T
+        const ptx::DescBase bQ = ptx::base_kmajor(aQ + (uint32_t)(n & 1) * kTileBytes);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(tmem + kColS + 64 * c, ptx::desc_at(bK, ptx::koff_kmajor(kk)),
-                         ptx::desc_at(bQ, ptx::koff_kmajor(kk)), idesc_s, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(tmem + kColDP + 64 * c, ptx::desc_at(bV, ptx::koff_kmajor(kk)),
-                         ptx::desc_at(bDO, ptx::koff_kmajor(kk)), idesc_s, kk > 0);
-        ptx::mma_commit(&sh->bar_sdp[c]);
+          ptx::mma_ss(tmem + kColS, ptx::desc_at(bK, ptx::koff_kmajor(kk)), ptx::desc_at(bQ, ptx::koff_kmajor(kk)),
+                      idesc_s, kk > 0);
+        ptx::mma_commit(&sh->bar_s);
       };
-      auto issue_acc = [&](int n, int c) {  // dV += P^T_c dO_c ; dK += dS^T_c Q_c  (four K steps of 16 query rows)
-        const uint32_t off = (uint32_t)(n & 1) * kTileBytes + (uint32_t)c * 4 * 2048u;
-        const ptx::DescBase bQt = ptx::base_mnmajor(aQ + off), bDOt = ptx::base_mnmajor(aDO + off);
+      auto issue_dp = [&](int n) {  // dP^T = V dO^T
+        const ptx::DescBase bDO = ptx::base_kmajor(aDO + (uint32_t)(n & 1) * kTileBytes);
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4)
-          ptx::mma_ts(tmem + kColDV, tmem + kColS + 64 * c + k4 * 8, ptx::desc_at(bDOt, ptx::koff_mnmajor(k4)),
-                         idesc_acc, 1);
+        for (int kk = 0; kk < D / 16; ++kk)
+          ptx::mma_ss(tmem + kColDP, ptx::desc_at(bV, ptx::koff_kmajor(kk)), ptx::desc_at(bDO, ptx::koff_kmajor(kk)),
+                      idesc_s, kk > 0);
+        ptx::mma_commit(&sh->bar_dp);
+      };
+      // A operand of the accumulation MMAs: packed bf16, 8 columns per K step of 16 query rows; warpgroup w wrote
+      // query columns [64w, 64w+64) at column offset 64w of the S^T / dP^T block
+      auto issue_dv = [&](int n) {  // dV += P^T dO
+        const ptx::DescBase bDOt = ptx::base_mnmajor(aDO + (uint32_t)(n & 1) * kTileBytes);
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4)
-          ptx::mma_ts(tmem + kColDK, tmem + kColDP + 64 * c + k4 * 8, ptx::desc_at(bQt, ptx::koff_mnmajor(k4)),
-                         idesc_acc, 1);
-        ptx::mma_commit(&sh->bar_acc[c]);
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          ptx::mma_ts(tmem + kColDV, tmem + kColS + 64 * (kk >> 2) + (kk & 3) * 8,
+                      ptx::desc_at(bDOt, ptx::koff_mnmajor(kk)), idesc_acc, 1);
+        ptx::mma_commit(&sh->bar_dofree[n & 1]);
+      };
+      auto issue_dk = [&](int n) {  // dK += dS^T Q
+        const ptx::DescBase bQt = ptx::base_mnmajor(aQ + (uint32_t)(n & 1) * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          ptx::mma_ts(tmem + kColDK, tmem + kColDP + 64 * (kk >> 2) + (kk & 3) * 8,
+                      ptx::desc_at(bQt, ptx::koff_mnmajor(kk)), idesc_acc, 1);
+        ptx::mma_commit(&sh->bar_qfree[n & 1]);
       };
       ok = ptx::mbar_wait(&sh->bar_kv, 0) && ptx::mbar_wait(&sh->bar_q[0], 0);
       if (ok) {
         ptx::tc_fence_after();
-        issue_sdp(0, 0);
-        issue_sdp(0, 1);
+        issue_s(0);
+        ok = ptx::mbar_wait(&sh->bar_do[0], 0);
+      }
+      if (ok) {
+        ptx::tc_fence_after();
+        issue_dp(0);
         ok = ptx::mbar_wait(&sh->bar_zero, 0);  // dK / dV columns zeroed
         if (!ok) fail_at = 7;
       }
       for (int n = 0; n < N && ok; ++n) {
         const uint32_t par = n & 1;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          ok = ptx::mbar_wait(&sh->bar_pds[c], par);
-          if (!ok) { fail_at = 2 + c; break; }
-          if (c == 0) FA_TRACE(0); else FA_TRACE(3);
+        const uint32_t par_next = ((n + 1) >> 1) & 1;
+        ok = ptx::mbar_wait(&sh->bar_p, par);  // P^T(n) is in tensor memory
+        if (!ok) { fail_at = 2; break; }
+        FA_TRACE(0);
+        ptx::tc_fence_after();
+        issue_dv(n);
+        FA_TRACE(1);
+        if (n + 1 < N) {
+          ok = ptx::mbar_wait(&sh->bar_q[(n + 1) & 1], par_next);
+          if (!ok) { fail_at = 3; break; }
           ptx::tc_fence_after();
-          issue_acc(n, c);
-          if (c == 1) ptx::mma_commit(&sh->bar_free[n & 1]);  // every MMA reading this Q/dO stage is issued
-          if (c == 0) FA_TRACE(1); else FA_TRACE(4);
-          if (n + 1 < N) {
-            if (c == 0) {
-              ok = ptx::mbar_wait(&sh->bar_q[(n + 1) & 1], ((n + 1) >> 1) & 1);
-              if (!ok) { fail_at = 4; break; }
-            }
-            // chain c's accumulation MMAs read P^T_c / dS^T_c from the columns the next S^T_c / dP^T_c overwrite.
-            // MMAs issued by one thread execute in issue order, so no wait for their completion is needed.
-            if (!kInOrderMma) {
-              ok = ptx::mbar_wait(&sh->bar_acc[c], par);
-              if (!ok) { fail_at = 5 + c; break; }
-            }
-            ptx::tc_fence_after();
-            issue_sdp(n + 1, c);
-            if (c == 0) FA_TRACE(2); else FA_TRACE(5);
-          }
+          issue_s(n + 1);
         }
+        FA_TRACE(2);
+        ok = ptx::mbar_wait(&sh->bar_ds, par);  // dS^T(n) is in tensor memory
+        if (!ok) { fail_at = 4; break; }
+        FA_TRACE(3);
+        ptx::tc_fence_after();
+        issue_dk(n);
+        FA_TRACE(4);
+        if (n + 1 < N) {
+          ok = ptx::mbar_wait(&sh->bar_do[(n + 1) & 1], par_next);
+          if (!ok) { fail_at = 5; break; }
+          ptx::tc_fence_after();
+          issue_dp(n + 1);
+        }
+        FA_TRACE(5);
       }
+      if (ok) ptx::mma_commit(&sh->bar_acc);
       if (!ok) give_up(abort_flag, P.status, 3, fail_at);
     }
   } else {
-    // ------------------------------------------------------------------ element-wise warpgroups (chain = tid / 128)
+    // ------------------------------------------------------------------ element-wise warpgroups
     const int row = tid & 127;        // key row inside the tile = TMEM lane
-    const int chain = tid >> 7;       // which 64 query columns of every tile this warpgroup handles
+    const int half = tid >> 7;        // which 64 query columns of every tile this warpgroup handles
     const int j = kt * kTile + row;   // global key position
     const bool row_ok = j < P.seq_k;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t colS = kColS + 64 * chain, colDP = kColDP + 64 * chain;
+    const uint32_t colS = kColS + 64 * half, colDP = kColDP + 64 * half;
     const float c2 = P.sm_scale * kLog2e;
     const float slope2 = (SK == FLEXATTN_SCORE_ALIBI) ? P.alibi_slopes[h] * kLog2e : 0.f;
     const float capl2 = P.cap * kLog2e;
     const float csc = (SK == FLEXATTN_SCORE_SOFTCAP) ? P.sm_scale / P.cap : 0.f;
     const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
     const int dj = (MK == FLEXATTN_MASK_DOCUMENT && row_ok) ? doc[j] : -2;
-    const size_t stat_base = (size_t)bh * P.seq_q;
     bool ok = true;
     int fail_at = 0;
 
@@ -273,83 +321,118 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t z[32];
 #pragma unroll
       for (int c = 0; c < 32; ++c) z[c] = 0u;
-      const uint32_t col = chain ? kColDV : kColDK;
+      const uint32_t col = half ? kColDV : kColDK;
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 32) ptx::tmem_st32(lane_base + col + c0, z);
       ptx::tmem_wait_st();
       ptx::tc_fence_before();
-      ptx::mbar_arrive(&sh->bar_zero);
+      ptx::mbar_arrive_warp(&sh->bar_zero);
     }
+
+    // Statistics of the query rows (l, m, delta, document id) are fetched from global memory one tile ahead
+    // into registers, so their latency is off the critical path.
+    const size_t stat_base = (size_t)bh * P.seq_q;
+    float pf_l = 0.f, pf_m = 0.f, pf_d = 0.f;
+    int pf_doc = -1;
+    bool pf_ok = false;
+    auto fetch_stats = [&](int n) {
+      const int i = (cm.x + n) * kTile + 64 * half + row;
+      pf_ok = i < P.seq_q;
+      if (pf_ok) {
+        pf_l = P.l[stat_base + i];
+        pf_m = P.m[stat_base + i];
+        pf_d = P.delta[stat_base + i];
+        if (MK == FLEXATTN_MASK_DOCUMENT) pf_doc = doc[i];
+      }
+    };
+    if (row < 64 && N > 0) fetch_stats(0);
 
     for (int n = 0; n < N; ++n) {
       const int st = n & 1;
-      const int qt = cm.x + n, i0 = qt * kTile + 64 * chain;  // first query position of this chain's columns
+      const int qt = cm.x + n, i0 = qt * kTile + 64 * half;  // first query position of this warpgroup's columns
       const bool partial = !(qt >= cm.z && qt < cm.w);
       if (row < 64) {
-        // statistics of this chain's 64 query rows (threads 0..63 of the warpgroup stage one row each)
-        const int i = i0 + row;
-        float nl = ptx::kRoundLog2, dl = 0.f;
-        if (i < P.seq_q) {
-          const float l = P.l[stat_base + i];
-          // l == 0 (fully masked row): force p to 0; kRoundLog2 pre-scales p for pack_bf16_trunc
-          nl = l > 0.f ? ptx::kRoundLog2 - fmaf(P.m[stat_base + i], kLog2e, log2f(l)) : -1.0e30f;
-          dl = P.delta[stat_base + i];
-        }
-        sh->nlse2[st][64 * chain + row] = nl;
-        sh->delta[st][64 * chain + row] = dl;
-        if (MK == FLEXATTN_MASK_DOCUMENT) sh->doc[st][64 * chain + row] = (i < P.seq_q) ? doc[i] : -1;
+        // threads 0..63 of the warpgroup stage one query row each
+        // l == 0 (fully masked row): force p to 0; kRoundLog2 pre-scales p for pack_bf16_trunc
+        sh->nlse2[st][64 * half + row] =
+            pf_ok ? (pf_l > 0.f ? ptx::kRoundLog2 - fmaf(pf_m, kLog2e, log2f(pf_l)) : -1.0e30f) : ptx::kRoundLog2;
+        sh->delta[st][64 * half + row] = pf_ok ? pf_d : 0.f;
+        if (MK == FLEXATTN_MASK_DOCUMENT) sh->doc[st][64 * half + row] = pf_ok ? pf_doc : -1;
+        if (n + 1 < N) fetch_stats(n + 1);
       }
-      ptx::named_bar_sync(1 + chain, 128);
-      if (tid == 0) FA_TRACE(8);
       // a failed wait never leaves the loop early: every thread keeps executing the same named barriers
-      if (ok) {
-        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_sdp[chain], n & 1));
-        if (!ok) fail_at = 10;
-      }
+      ptx::named_bar_sync(1 + half, 128);
+      if (tid == 0) FA_TRACE(8);
       if (!ok) continue;
+      float st0[32], st1[32];
+      load_stats32(st0, &sh->nlse2[st][64 * half]);
+      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_s, n & 1));
+      if (!ok) { fail_at = 10; continue; }
       if (tid == 0) FA_TRACE(9);
       ptx::tc_fence_after();
-      uint32_t sr[2][32], pr[2][32];
+      uint32_t sr[2][32];
       ptx::tmem_ld32(lane_base + colS, sr[0]);
       ptx::tmem_ld32(lane_base + colS + 32, sr[1]);
-      ptx::tmem_ld32(lane_base + colDP, pr[0]);
-      ptx::tmem_ld32(lane_base + colDP + 32, pr[1]);
+      load_stats32(st1, &sh->nlse2[st][64 * half + 32]);
       ptx::tmem_wait_ld();
       ptx::tmem_ld_acquire(sr[0]);
       ptx::tmem_ld_acquire(sr[1]);
-      ptx::tmem_ld_acquire(pr[0]);
-      ptx::tmem_ld_acquire(pr[1]);
+      if (tid == 0) FA_TRACE(13);
+      {
+        uint32_t pk_p[32];
+        const float abase = slope2 * (float)(j - i0);  // ALiBi bias = slope * (j - i), i = i0 + column
+        if (partial) {
+          dkv_p_math32<SK, MK, true>(sr[0], pk_p, st0, &sh->doc[st][64 * half], i0, j, dj, P.seq_q, P.window,
+                                     P.stride, c2, slope2, abase, capl2, csc);
+          dkv_p_math32<SK, MK, true>(sr[1], pk_p + 16, st1, &sh->doc[st][64 * half + 32], i0 + 32, j, dj, P.seq_q,
+                                     P.window, P.stride, c2, slope2, abase - 32.f * slope2, capl2, csc);
+        } else {
+          dkv_p_math32<SK, MK, false>(sr[0], pk_p, st0, &sh->doc[st][64 * half], i0, j, dj, P.seq_q, P.window,
+                                      P.stride, c2, slope2, abase, capl2, csc);
+          dkv_p_math32<SK, MK, false>(sr[1], pk_p + 16, st1, &sh->doc[st][64 * half + 32], i0 + 32, j, dj, P.seq_q,
+                                      P.window, P.stride, c2, slope2, abase - 32.f * slope2, capl2, csc);
+        }
+        if (tid == 0) FA_TRACE(14);
+        ptx::tmem_st32(lane_base + colS, pk_p);  // bf16 P^T over the first half of this warpgroup's S^T columns
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive_warp(&sh->bar_p);
+      }
       if (tid == 0) FA_TRACE(10);
-      uint32_t pk_p[32], pk_ds[32];
-      const float abase = slope2 * (float)(j - i0);  // ALiBi bias = slope * (j - i), i = i0 + column
-      if (partial)
-        dkv_half_math<SK, MK, true>(sr, pr, pk_p, pk_ds, &sh->nlse2[st][64 * chain], &sh->delta[st][64 * chain],
-                                    &sh->doc[st][64 * chain], i0, j, dj, P.seq_q, P.window, P.stride, c2, slope2,
-                                    abase, capl2, csc);
-      else
-        dkv_half_math<SK, MK, false>(sr, pr, pk_p, pk_ds, &sh->nlse2[st][64 * chain], &sh->delta[st][64 * chain],
-                                     &sh->doc[st][64 * chain], i0, j, dj, P.seq_q, P.window, P.stride, c2, slope2,
-                                     abase, capl2, csc);
-      ptx::tmem_st32(lane_base + colS, pk_p);
-      ptx::tmem_st32(lane_base + colDP, pk_ds);
+      load_stats32(st0, &sh->delta[st][64 * half]);
+      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dp, n & 1));
+      if (!ok) { fail_at = 11; continue; }
       if (tid == 0) FA_TRACE(11);
-      ptx::tmem_wait_st();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(&sh->bar_pds[chain]);
+      ptx::tc_fence_after();
+      {
+        uint32_t pr[32], pk_ds[32];
+        ptx::tmem_ld32(lane_base + colDP, pr);
+        load_stats32(st1, &sh->delta[st][64 * half + 32]);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld_acquire(pr);
+        if (tid == 0) FA_TRACE(15);
+        dkv_ds_math32(sr[0], pr, pk_ds, st0);
+        ptx::tmem_ld32(lane_base + colDP + 32, pr);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld_acquire(pr);
+        dkv_ds_math32(sr[1], pr, pk_ds + 16, st1);
+        ptx::tmem_st32(lane_base + colDP, pk_ds);
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive_warp(&sh->bar_ds);
+      }
       if (tid == 0) FA_TRACE(12);
     }
 
     if (ok && N > 0) {
-      // both chains' accumulation MMAs of the last tile must have completed
-      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_acc[0], (N - 1) & 1) &&
-                                       ptx::mbar_wait(&sh->bar_acc[1], (N - 1) & 1));
+      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_acc, 0));  // every accumulation MMA has completed
       if (!ok) fail_at = 12;
     }
     if (ok) {
       if (N > 0) ptx::tc_fence_after();
       const size_t grow = (size_t)bh * P.seq_k + j;
       {
-        const int which = chain;  // warpgroup 0 stores dK, warpgroup 1 stores dV
+        const int which = half;  // warpgroup 0 stores dK, warpgroup 1 stores dV
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(which ? P.dv : P.dk) + grow * D;
         const float sc = which ? 1.f : P.sm_scale;
         const uint32_t col = which ? kColDV : kColDK;

@@ -64,6 +64,30 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
 }
 
+// One arrival per WARP instead of one per thread: an arrive is a shared-memory atomic, and 32 of them to one
+// address serialise.  Every lane has completed its part (its own tcgen05.wait / fence, then the warp barrier,
+// which orders memory among the lanes); lane 0's arrive then publishes the whole warp's work.  Barriers used
+// this way are initialised with the number of arriving WARPS.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+
+// The same wait for threads whose wake-up latency does not matter (producers waiting for a free stage): they
+// sleep between polls, so that their polling does not take issue slots from the warps that share their scheduler.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, unsigned sleep_ns = 100) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int it = 0; it < 256; ++it) {
+      __nanosleep(sleep_ns);
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+  }
+}
+
 // ------------------------------------------------------------------ TMA (no multicast anywhere)
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
