@@ -69,7 +69,24 @@ def build(verbose: bool = False, jobs: int | None = None) -> str:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    if not DEFINES:
+        _build_driver()
     return LIB
+
+
+def _build_driver():
+    """flexattn_bench: the stand-alone C++ driver over the C ABI (csrc/flexattn_bench.cpp), linked against the
+    library next to it."""
+    src = os.path.join(CSRC, "flexattn_bench.cpp")
+    exe = os.path.join(PKG, "flexattn_bench")
+    if os.path.exists(exe) and os.path.getmtime(exe) >= max(os.path.getmtime(src), os.path.getmtime(LIB)):
+        return exe
+    cmd = [NVCC, "-O2", "-std=c++17", "-I", os.path.join(PKG, "..", "include"), src, "-o", exe, "-L", PKG, "-lflexattn",
+           "-cudart", "shared", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"driver build failed:\n{r.stdout}\n{r.stderr}")
+    return exe
 
 
 if __name__ == "__main__":
