@@ -1,54 +1,109 @@
-// Forward flex attention, software-pipelined variant for long rows (sm_100a).
+// Forward flex attention, persistent software-pipelined kernel (sm_100a).
 //
-// Same math and interface as fwd_sm100.cu (reference: flex_attention_kernel.py:196-327) but one CTA per SM
-// keeps THREE score tiles in flight in tensor memory so that the tensor core and the softmax never wait
-// for each other:
+// Same math and interface as fwd_sm100.cu (reference: flex_attention_kernel.py:196-327).  One CTA per SM stays
+// resident and walks a list of work items (q tile, batch*head), heaviest q tiles first, item w going to CTA
+// w mod gridDim.x.  Inside a CTA the kv tiles of all its items form ONE stream, numbered T = 0, 1, 2 ...: the
+// K/V rings, the three score buffers and every barrier phase are indexed by T, so the loads and the Q K^T MMAs
+// of the next item start while the softmax and the epilogue of the current one are still running, and the
+// per-item prologue (loads in flight, first scores) and epilogue (normalise, store) cost no tensor-core time.
 //
-//   warp 8, lane 0 : MMA issuer.  S[t % 3] = Q K[t]^T runs up to three kv tiles ahead of the softmax;
-//                    O += P[n] V[n] is issued as soon as the softmax has written P[n] over S[n % 3].
-//   warp 9, lane 0 : TMA producer.  Q once; K and V through two-stage rings, each refilled as soon as the
-//                    MMA that read the stage has completed (tcgen05.commit -> mbarrier).
+//   warp 8, lane 0 : MMA issuer.  S[T % 3] = Q K[T]^T runs up to three kv tiles ahead of the softmax;
+//                    O += P[T] V[T] is issued as soon as the softmax has written P[T] over S[T % 3].
+//   warp 9, lane 0 : TMA producer for Q (two stages, one per item in flight) and K (two-stage ring).
+//   warp 10, lane 0: TMA producer for V (two-stage ring).  Each ring stage is refilled as soon as the MMA that
+//                    read it has completed (tcgen05.commit -> mbarrier).
 //   warps 0..7     : softmax, two warpgroups.  Threads t and t + 128 share query row t (= TMEM lane t)
 //                    and take one 64-column half of every score tile each; partial row maxima are
 //                    exchanged through shared memory; P goes back to tensor memory as packed bf16; O is
-//                    rescaled in tensor memory only when the running max moved by more than 2^8.
+//                    rescaled in tensor memory only when the running max moved by more than 2^8.  After an
+//                    item's last tile they read O out of tensor memory, normalise and store it, and go on
+//                    to the next item; the first P V of that item is issued only after they have written
+//                    its first P, i.e. after they are done reading the previous O.
 //
-// Tensor memory: S0, S1, S2 (3 x 128 columns) + O (D columns) = 512 for D = 128.  Shared memory: Q + 2 K +
-// 2 V tiles (160 KB for D = 128).
+// Tensor memory: S0, S1, S2 (3 x 128 columns) + O (D columns) = 512 for D = 128.  Shared memory: 2 Q + 2 K +
+// 2 V tiles (192 KB for D = 128).
 #include "sm100.cuh"
 
-#ifdef FLEXATTN_TRACE
-#define FA_TRACE(slot)                                                          \
-  do {                                                                          \
-    if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64)     \
-      P.trace[n * 16 + (slot)] = clock64();                                     \
-  } while (0)
-#define FA_MARK(slot)                                                           \
-  do {                                                                          \
-    if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0)               \
-      P.trace[63 * 16 + (slot)] = clock64();                                    \
-  } while (0)
-#else
-#define FA_TRACE(slot)
-#define FA_MARK(slot)
-#endif
 
 namespace flexattn {
 namespace {
 
-constexpr int kThreads = 320;
-constexpr int kMmaWarp = 8, kTmaWarp = 9;
+constexpr int kThreads = 352;
+constexpr int kMmaWarp = 8, kTmaWarp = 9, kTmaWarpV = 10;
 constexpr int kHalf = kTile / 2;
 constexpr int kSBufs = 3;
 constexpr float kLazyRescale = 8.0f;  // log2 units
-constexpr bool kInOrderMma = true;     // rely on issue-order execution of one thread's tcgen05.mma stream
 
 struct PipeSmem {
-  uint64_t bar_q, bar_k[2], bar_v[2], bar_kfree[2], bar_s[kSBufs], bar_p[kSBufs], bar_pv[2];
+  uint64_t bar_q[2], bar_qfree[2], bar_k[2], bar_v[2], bar_kfree[2], bar_s[kSBufs], bar_p[kSBufs], bar_pv[kSBufs];
   uint32_t tmem_base;
+  int32_t item_tiles[8];  // kv tiles of the CTA's non-empty items (ring; -1 ends the list), producer -> MMA issuer
   float pmax[2][2][kTile];  // [tile parity][column half][row]
   float lsum[2][kTile];     // [column half][row]
   int32_t doc[2][kTile];
+};
+
+// A CTA's walk over its work items.  The (batch*head) slices are taken in groups small enough for the K and V
+// of a whole group to stay in L2 (every q tile of a slice re-reads them); inside a group the items are ordered by q
+// tile from the LAST one (the heaviest under a causal mask) down, slice index fastest.  The resulting list is dealt
+// to the CTAs in rounds that alternate direction (CTA c takes entry c of an even round and entry G-1-c of an odd
+// one), which evens out the work of a sorted list.  The mask-map row of the next item is fetched one item ahead.
+struct ItemCursor {
+  const DevParams& P;
+  int total, bh_count, group, per_group;
+  int round, w;      // current round and item; valid while w < total
+  int4 rm, rm_next;  // mask-map rows {first kv tile, end kv tile, first full, end full} of this item and the next
+  int bh_, qt_;
+  __device__ __forceinline__ int item_of(int r) const {
+    const int G = (int)gridDim.x, c = (int)blockIdx.x;
+    return r * G + ((r & 1) ? G - 1 - c : c);
+  }
+  __device__ __forceinline__ void locate(int item, int& bh, int& qt) const {
+    const int g = item / per_group, r = item - g * per_group;
+    const int first = g * group;
+    const int width = min(group, bh_count - first);  // slices in this group (the last one may be smaller)
+    const int rank = r / width;
+    bh = first + (r - rank * width);
+    qt = P.n_qt - 1 - rank;
+  }
+  __device__ __forceinline__ int4 fetch(int item) const {
+    int bh, qt;
+    locate(item, bh, qt);
+    return __ldg(&P.row_map[(size_t)(P.map_rows > 1 ? bh / P.heads : 0) * P.n_qt + qt]);
+  }
+  __device__ __forceinline__ ItemCursor(const DevParams& p) : P(p) {
+    bh_count = p.batch * p.heads;
+    total = p.n_qt * bh_count;
+    // K + V of one slice: 2 * seq_k * head_dim * 2 bytes; keep about 48 MB of them live
+    const long long slice_bytes = 4ll * p.seq_k * p.head_dim;
+    group = (int)max(1ll, min((long long)bh_count, (48ll << 20) / slice_bytes));
+    per_group = group * p.n_qt;
+    round = 0;
+    w = item_of(0);
+    rm = rm_next = make_int4(0, 0, 0, 0);
+    bh_ = qt_ = 0;
+    if (w < total) {
+      rm = fetch(w);
+      locate(w, bh_, qt_);
+    }
+    if (item_of(1) < total) rm_next = fetch(item_of(1));
+  }
+  __device__ __forceinline__ bool valid() const { return w < total; }
+  __device__ __forceinline__ int tiles() const { return rm.y - rm.x; }
+  __device__ __forceinline__ int bh() const { return bh_; }
+  __device__ __forceinline__ int qt() const { return qt_; }
+  __device__ __forceinline__ void next() {
+    ++round;
+    w = item_of(round);
+    rm = rm_next;
+    if (w < total) locate(w, bh_, qt_);
+    const int nxt = item_of(round + 1);
+    if (nxt < total) rm_next = fetch(nxt);
+  }
+  // skip items without any kv tile (the producers and the MMA issuer have nothing to do for them)
+  __device__ __forceinline__ void skip_empty() {
+    while (valid() && tiles() <= 0) next();
+  }
 };
 
 // x: this thread's 64 raw scores (columns c_base .. c_base+63 of the tile) -> log2-domain logits in place;
@@ -92,30 +147,25 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;
-  uint8_t* sK = smem + kTileBytes;      // two stages
-  uint8_t* sV = smem + 3 * kTileBytes;  // two stages
-  PipeSmem* sh = reinterpret_cast<PipeSmem*>(smem + 5 * kTileBytes);
+  uint8_t* sQ = smem;                   // two stages
+  uint8_t* sK = smem + 2 * kTileBytes;  // two stages
+  uint8_t* sV = smem + 4 * kTileBytes;  // two stages
+  PipeSmem* sh = reinterpret_cast<PipeSmem*>(smem + 6 * kTileBytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) FA_MARK(0);
-  const int qt = P.n_qt - 1 - (int)blockIdx.x;  // heavy (late) causal tiles first
-  const int bh = blockIdx.y, b = bh / P.heads, h = bh % P.heads;
-  const int4 rm = P.row_map[(size_t)(P.map_rows > 1 ? b : 0) * P.n_qt + qt];
-  const int N = rm.y - rm.x;
 
   if (*reinterpret_cast<volatile int*>(abort_flag) != 0) return;
-  if (tid == 0) FA_MARK(1);
 
   if (tid == 0) {
-    ptx::mbar_init(&sh->bar_q, 1);
     for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(&sh->bar_q[s], 1);
+      ptx::mbar_init(&sh->bar_qfree[s], 1);
       ptx::mbar_init(&sh->bar_k[s], 1);
       ptx::mbar_init(&sh->bar_v[s], 1);
       ptx::mbar_init(&sh->bar_kfree[s], 1);
-      ptx::mbar_init(&sh->bar_pv[s], 1);
     }
     for (int s = 0; s < kSBufs; ++s) {
+      ptx::mbar_init(&sh->bar_pv[s], 1);
       ptx::mbar_init(&sh->bar_s[s], 1);
       ptx::mbar_init(&sh->bar_p[s], 256);
     }
@@ -129,118 +179,148 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
-  if (tid == 0) FA_MARK(2);
 
+  // bar_pv has one barrier per SCORE buffer (three), not per V stage: the softmax warpgroups wait on it only now and
+  // then (lazy rescale, item epilogue) and may be up to three tiles ahead of the P V MMAs; a wait by parity is only
+  // unambiguous while the waiter is less than two completions ahead of the barrier, and with barrier T % 3 the
+  // previous completion, P V of tile T-3, is known to be done once S of tile T has been read.
+  // In every role: T = index of a kv tile in this CTA's stream over all its items, qi = index of an item among
+  // the CTA's non-empty items.  Ring stage = index & 1, barrier phase = (index >> 1) & 1 (score buffers: % 3, / 3).
   if (warp == kTmaWarp) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && N > 0) {
+    // ------------------------------------------------------------------ TMA producer: Q and K
+    if (lane == 0) {
       bool ok = true;
       int fail_at = 0;
       ptx::prefetch_tensormap(&tm_q);
       ptx::prefetch_tensormap(&tm_k);
-      ptx::prefetch_tensormap(&tm_v);
-      auto load_k = [&](int t) {
-        uint8_t* dst = sK + (t & 1) * kTileBytes;
-        ptx::mbar_arrive_expect_tx(&sh->bar_k[t & 1], kTileBytes);
+      int T = 0, qi = 0;
+      for (ItemCursor it(P); ok; it.next(), ++qi) {
+        it.skip_empty();
+        if (!it.valid()) break;
+        const int bh = it.bh(), first = it.rm.x, N = it.tiles();
+        if (qi >= 2) {  // the stage held the Q tile of item qi-2: all of its Q K^T MMAs must have completed
+          ok = ptx::mbar_wait(&sh->bar_qfree[qi & 1], ((qi - 2) >> 1) & 1);
+          if (!ok) { fail_at = 20; break; }
+        }
+        sh->item_tiles[qi & 7] = N;  // read by the MMA issuer after it has waited on bar_q (release / acquire)
+        ptx::mbar_arrive_expect_tx(&sh->bar_q[qi & 1], kTileBytes);
 #pragma unroll
         for (int p = 0; p < kPanels; ++p)
-          ptx::tma_load_3d(dst + p * ptx::kPanelBytes, &tm_k, &sh->bar_k[t & 1], p * 64, (rm.x + t) * kTile, bh);
-      };
-      auto load_v = [&](int t) {
-        uint8_t* dst = sV + (t & 1) * kTileBytes;
-        ptx::mbar_arrive_expect_tx(&sh->bar_v[t & 1], kTileBytes);
+          ptx::tma_load_3d(sQ + (qi & 1) * kTileBytes + p * ptx::kPanelBytes, &tm_q, &sh->bar_q[qi & 1], p * 64,
+                           it.qt() * kTile, bh);
+        for (int t = 0; t < N; ++t, ++T) {
+          if (T >= 2) {  // K[T] replaces K[T-2], read by Q K^T of tile T-2
+            ok = ptx::mbar_wait(&sh->bar_kfree[T & 1], ((T - 2) >> 1) & 1);
+            if (!ok) { fail_at = 21; break; }
+          }
+          ptx::mbar_arrive_expect_tx(&sh->bar_k[T & 1], kTileBytes);
 #pragma unroll
-        for (int p = 0; p < kPanels; ++p)
-          ptx::tma_load_3d(dst + p * ptx::kPanelBytes, &tm_v, &sh->bar_v[t & 1], p * 64, (rm.x + t) * kTile, bh);
-      };
-      ptx::mbar_arrive_expect_tx(&sh->bar_q, kTileBytes);
-#pragma unroll
-      for (int p = 0; p < kPanels; ++p)
-        ptx::tma_load_3d(sQ + p * ptx::kPanelBytes, &tm_q, &sh->bar_q, p * 64, qt * kTile, bh);
-      load_k(0);
-      if (N > 1) load_k(1);
-      load_v(0);
-      if (N > 1) load_v(1);
-      FA_MARK(3);
-      // K[t] for t = 2..4 replaces K[t-2], read by the Q K^T MMAs the issuer runs ahead of the softmax
-      for (int t = 2; t < 5 && t < N && ok; ++t) {
-        ok = ptx::mbar_wait(&sh->bar_kfree[t & 1], ((t - 2) >> 1) & 1);
-        if (!ok) { fail_at = 20; break; }
-        load_k(t);
+          for (int p = 0; p < kPanels; ++p)
+            ptx::tma_load_3d(sK + (T & 1) * kTileBytes + p * ptx::kPanelBytes, &tm_k, &sh->bar_k[T & 1], p * 64,
+                             (first + t) * kTile, bh);
+        }
       }
-      for (int n = 0; n < N && ok; ++n) {
-        if (n + 2 < N) {  // V[n+2] replaces V[n], read by P V of tile n
-          ok = ptx::mbar_wait(&sh->bar_pv[n & 1], (n >> 1) & 1);
-          if (!ok) { fail_at = 21; break; }
-          load_v(n + 2);
-        }
-        if (n + 5 < N) {  // K[n+5] replaces K[n+3], read by Q K^T of tile n+3
-          ok = ptx::mbar_wait(&sh->bar_kfree[(n + 3) & 1], ((n + 3) >> 1) & 1);
-          if (!ok) { fail_at = 22; break; }
-          load_k(n + 5);
-        }
+      if (ok) {  // end of the list: one more completion of the Q barrier, carrying the terminator
+        sh->item_tiles[qi & 7] = -1;
+        ptx::mbar_arrive(&sh->bar_q[qi & 1]);
       }
       if (!ok) give_up(abort_flag, P.status, 4, fail_at);
     }
+  } else if (warp == kTmaWarpV) {
+    // ------------------------------------------------------------------ TMA producer: V
+    if (lane == 0) {
+      bool ok = true;
+      ptx::prefetch_tensormap(&tm_v);
+      int T = 0;
+      uint32_t wsb = 0, wph = 0;  // barrier (T-2) % 3 and phase ((T-2) / 3) & 1 of the P V this thread waits for
+      for (ItemCursor it(P); ok; it.next()) {
+        it.skip_empty();
+        if (!it.valid()) break;
+        const int bh = it.bh(), first = it.rm.x, N = it.tiles();
+        for (int t = 0; t < N; ++t, ++T) {
+          if (T >= 2) {  // V[T] replaces V[T-2], read by P V of tile T-2
+            ok = ptx::mbar_wait(&sh->bar_pv[wsb], wph);
+            if (!ok) break;
+            if (++wsb == kSBufs) { wsb = 0; wph ^= 1u; }
+          }
+          ptx::mbar_arrive_expect_tx(&sh->bar_v[T & 1], kTileBytes);
+#pragma unroll
+          for (int p = 0; p < kPanels; ++p)
+            ptx::tma_load_3d(sV + (T & 1) * kTileBytes + p * ptx::kPanelBytes, &tm_v, &sh->bar_v[T & 1], p * 64,
+                             (first + t) * kTile, bh);
+        }
+      }
+      if (!ok) give_up(abort_flag, P.status, 4, 23);
+    }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && N > 0) {
+    // Two positions in the tile stream: `q*` for the next Q K^T (three tiles ahead) and `p*` for the next P V.
+    // Q K^T of tile T+3 overwrites the columns P V of tile T reads its A operand from: MMAs issued by one thread
+    // execute in issue order, so issuing it after that P V is all the protection needed.  The first P V of an
+    // item overwrites O: the softmax warpgroups have read the previous item's O before they write that tile's P.
+    if (lane == 0) {
       bool ok = true;
       int fail_at = 1;
       constexpr uint32_t idesc_qk = ptx::make_idesc(128, 128, false);
       constexpr uint32_t idesc_pv = ptx::make_idesc(128, D, true);
-      const ptx::DescBase bQ = ptx::base_kmajor(ptx::smem_u32(sQ));
+      const uint32_t aQ = ptx::smem_u32(sQ);
       const ptx::DescBase bK0 = ptx::base_kmajor(ptx::smem_u32(sK)), bK1 = ptx::base_kmajor(ptx::smem_u32(sK + kTileBytes));
       const ptx::DescBase bV0 = ptx::base_mnmajor(ptx::smem_u32(sV)), bV1 = ptx::base_mnmajor(ptx::smem_u32(sV + kTileBytes));
-      auto issue_qk = [&](int t) {
-        const ptx::DescBase bk = (t & 1) ? bK1 : bK0;
-        const uint32_t dS = tmem + (uint32_t)(t % kSBufs) * 128u;
+      // This thread's instruction count per MMA bounds the whole pipeline, so it does no index arithmetic of its own:
+      // the number of tiles of each item comes from the producer through item_tiles (valid once bar_q of the item
+      // has completed), and score buffer (T % 3) and barrier phase ((T / 3) & 1) are kept as counters.
+      int qT = 0, qn = 0, qqi = 0, qN = 0;  // Q K^T position: stream index, tile inside the item, item index, its tiles
+      int pT = 0, pn = 0, pqi = 0, pN = 0;  // P V position
+      bool q_end = false;
+      uint32_t qsb = 0, psb = 0, psph = 0;
+      const ptx::DescBase bQ0 = ptx::base_kmajor(aQ), bQ1 = ptx::base_kmajor(aQ + kTileBytes);
+      auto issue_qk = [&]() {  // one tile at the Q K^T position, then advance it
+        if (qn == 0) {
+          ok = ptx::mbar_wait(&sh->bar_q[qqi & 1], (qqi >> 1) & 1);
+          if (!ok) { fail_at = 2; return; }
+          qN = sh->item_tiles[qqi & 7];
+          if (qN < 0) { q_end = true; return; }
+        }
+        ok = ptx::mbar_wait(&sh->bar_k[qT & 1], (qT >> 1) & 1);
+        if (!ok) { fail_at = 3; return; }
+        ptx::tc_fence_after();
+        const ptx::DescBase bq = (qqi & 1) ? bQ1 : bQ0;
+        const ptx::DescBase bk = (qT & 1) ? bK1 : bK0;
+        const uint32_t dS = tmem + qsb * 128u;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(dS, ptx::desc_at(bQ, ptx::koff_kmajor(kk)), ptx::desc_at(bk, ptx::koff_kmajor(kk)), idesc_qk, kk > 0);
-        ptx::mma_commit(&sh->bar_s[t % kSBufs]);
-        ptx::mma_commit(&sh->bar_kfree[t & 1]);
+          ptx::mma_ss(dS, ptx::desc_at(bq, ptx::koff_kmajor(kk)), ptx::desc_at(bk, ptx::koff_kmajor(kk)), idesc_qk, kk > 0);
+        ptx::mma_commit(&sh->bar_s[qsb]);
+        ptx::mma_commit(&sh->bar_kfree[qT & 1]);
+        ++qT;
+        if (++qsb == kSBufs) qsb = 0;
+        if (++qn == qN) {
+          ptx::mma_commit(&sh->bar_qfree[qqi & 1]);
+          qn = 0;
+          ++qqi;
+        }
       };
-      ok = ptx::mbar_wait(&sh->bar_q, 0);
-      FA_MARK(4);
-      for (int t = 0; t < kSBufs && t < N && ok; ++t) {
-        ok = ptx::mbar_wait(&sh->bar_k[t & 1], (t >> 1) & 1);
-        if (!ok) { fail_at = 2; break; }
-        ptx::tc_fence_after();
-        if (t == 0) FA_MARK(5);
-        issue_qk(t);
-      }
-      for (int n = 0; n < N && ok; ++n) {
-        const int sb = n % kSBufs;
-        ok = ptx::mbar_wait(&sh->bar_p[sb], (n / kSBufs) & 1);
-        if (!ok) { fail_at = 3; break; }
-        FA_TRACE(0);
-        ok = ptx::mbar_wait(&sh->bar_v[n & 1], (n >> 1) & 1);
+      for (int t = 0; t < kSBufs && ok && !q_end; ++t) issue_qk();
+      while (ok && pT < qT) {  // every tile whose Q K^T has been issued gets its P V
+        if (pn == 0) pN = sh->item_tiles[pqi & 7];  // written before the Q K^T position passed this item
+        ok = ptx::mbar_wait(&sh->bar_p[psb], psph);
         if (!ok) { fail_at = 4; break; }
-        FA_TRACE(1);
+        ok = ptx::mbar_wait(&sh->bar_v[pT & 1], (pT >> 1) & 1);
+        if (!ok) { fail_at = 5; break; }
         ptx::tc_fence_after();
-        const ptx::DescBase bv = (n & 1) ? bV1 : bV0;
+        const ptx::DescBase bv = (pT & 1) ? bV1 : bV0;
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
-          ptx::mma_ts(tmem + kColO, tmem + (uint32_t)sb * 128u + kk * 8, ptx::desc_at(bv, ptx::koff_mnmajor(kk)), idesc_pv,
-                      (n > 0) || (kk > 0));
-        ptx::mma_commit(&sh->bar_pv[n & 1]);
-        FA_TRACE(2);
-        if (n + kSBufs < N) {
-          // Q K^T of tile n+3 overwrites the columns P V of tile n reads its A operand from.  MMAs issued by one
-          // thread execute in issue order, so no wait for P V to complete is needed between the two.
-          if (!kInOrderMma) {
-            ok = ptx::mbar_wait(&sh->bar_pv[n & 1], (n >> 1) & 1);
-            if (!ok) { fail_at = 5; break; }
-          }
-          FA_TRACE(3);
-          ok = ptx::mbar_wait(&sh->bar_k[(n + kSBufs) & 1], ((n + kSBufs) >> 1) & 1);
-          if (!ok) { fail_at = 6; break; }
-          FA_TRACE(4);
-          ptx::tc_fence_after();
-          issue_qk(n + kSBufs);
-          FA_TRACE(5);
+          ptx::mma_ts(tmem + kColO, tmem + psb * 128u + kk * 8, ptx::desc_at(bv, ptx::koff_mnmajor(kk)), idesc_pv,
+                      (pn > 0) || (kk > 0));
+        ptx::mma_commit(&sh->bar_pv[psb]);
+        ++pT;
+        if (++psb == kSBufs) { psb = 0; psph ^= 1u; }
+        if (++pn == pN) {
+          pn = 0;
+          ++pqi;
         }
+        if (!q_end) issue_qk();
       }
       if (!ok) give_up(abort_flag, P.status, 4, fail_at);
     }
@@ -249,190 +329,204 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int row = tid & 127;
     const int half = tid >> 7;
     const int c_base = half * kHalf;
-    const int i = qt * kTile + row;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float c2 = P.sm_scale * kLog2e;
-    const float slope2 = (SK == FLEXATTN_SCORE_ALIBI) ? P.alibi_slopes[h] * kLog2e : 0.f;
     const float capl2 = P.cap * kLog2e;
     const float csc = (SK == FLEXATTN_SCORE_SOFTCAP) ? P.sm_scale / P.cap : 0.f;
-    const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
-    const int di = (MK == FLEXATTN_MASK_DOCUMENT && i < P.seq_q) ? doc[i] : 0;
-    float m_ref = kMasked, m_true = kMasked, l = 0.f;  // l: sum over this thread's columns only
     bool ok = true;
     int fail_at = 0;
+    int T = 0;  // stream index of the next kv tile
+    int sb = 0;          // T % 3: score buffer of that tile
+    uint32_t sph = 0;    // (T / 3) & 1: phase of its barriers
 
-    for (int n = 0; n < N; ++n) {
-      const uint32_t par = n & 1;
-      const int sb = n % kSBufs;
-      const uint32_t colS = (uint32_t)sb * 128u;
-      const int kt = rm.x + n, j0 = kt * kTile;
-      const bool partial = !(kt >= rm.z && kt < rm.w);
-      if (MK == FLEXATTN_MASK_DOCUMENT && partial && half == 0) {
-        const int j = j0 + row;
-        sh->doc[par][row] = (j < P.seq_k) ? doc[j] : -1;
-      }
-      // A failed wait never leaves the loop early: every thread keeps executing the same named barriers so
-      // that nobody is left waiting on one (the time-out path must not be able to hang either).
-      if (ok) {
-        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_s[sb], (n / kSBufs) & 1));
-        if (!ok) fail_at = 10;
-      }
-      if (tid == 0) FA_TRACE(8);
-      if (tid == 0 && n == 0) FA_MARK(6);
-      float x[kHalf];
-      if (ok) {
-        ptx::tc_fence_after();
-        uint32_t xr[2][32];
-#pragma unroll
-        for (int q2 = 0; q2 < 2; ++q2) ptx::tmem_ld32(lane_base + colS + c_base + q2 * 32, xr[q2]);
-        ptx::tmem_wait_ld();
-#pragma unroll
-        for (int q2 = 0; q2 < 2; ++q2) {
-          ptx::tmem_ld_acquire(xr[q2]);
-#pragma unroll
-          for (int c = 0; c < 32; ++c) x[q2 * 32 + c] = __uint_as_float(xr[q2][c]);
+    for (ItemCursor it(P); it.valid(); it.next()) {
+      const int qt = it.qt(), bh = it.bh(), b = bh / P.heads, h = bh % P.heads;
+      const int4 rm = it.rm;
+      const int N = rm.y - rm.x;
+      const int i = qt * kTile + row;
+      const float slope2 = (SK == FLEXATTN_SCORE_ALIBI) ? P.alibi_slopes[h] * kLog2e : 0.f;
+      const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
+      const int di = (MK == FLEXATTN_MASK_DOCUMENT && i < P.seq_q) ? doc[i] : 0;
+      float m_ref = kMasked, m_true = kMasked, l = 0.f;  // l: sum over this thread's columns only
+
+      for (int n = 0; n < N; ++n, ++T) {
+        const uint32_t par = T & 1;
+        const uint32_t colS = (uint32_t)sb * 128u;
+        const int kt = rm.x + n, j0 = kt * kTile;
+        const bool partial = !(kt >= rm.z && kt < rm.w);
+        if (MK == FLEXATTN_MASK_DOCUMENT && partial && half == 0) {
+          const int j = j0 + row;
+          sh->doc[par][row] = (j < P.seq_k) ? doc[j] : -1;
         }
-      }
-      if (tid == 0) FA_TRACE(9);
-      if (MK == FLEXATTN_MASK_DOCUMENT && partial) ptx::named_bar_sync(2, 256);  // kv-tile document ids visible
-      // xs: factor still to be applied to x inside the exp2 argument (the plain-score fast path keeps the raw
-      // scores and folds sm_scale*log2e into the FMA that also subtracts the running max)
-      float tmax = kMasked, xs = 1.0f;
-      if (ok) {
-        if (partial) {
-          tmax = score_half<SK, MK, true>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di,
-                                          sh->doc[par]);
-        } else if constexpr (SK != FLEXATTN_SCORE_NONE) {
-          tmax = score_half<SK, MK, false>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di,
-                                           sh->doc[par]);
-        } else {
-          float mx[4] = {x[0], x[1], x[2], x[3]};
+        // A failed wait never leaves the loops early: every thread keeps executing the same named barriers so
+        // that nobody is left waiting on one (the time-out path must not be able to hang either).
+        if (ok) {
+          ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_s[sb], sph));
+          if (!ok) fail_at = 10;
+        }
+        float x[kHalf];
+        if (ok) {
+          ptx::tc_fence_after();
+          uint32_t xr[2][32];
 #pragma unroll
-          for (int c = 4; c + 7 < kHalf; c += 8) {
-            mx[0] = ptx::max3(mx[0], x[c], x[c + 1]);
-            mx[1] = ptx::max3(mx[1], x[c + 2], x[c + 3]);
-            mx[2] = ptx::max3(mx[2], x[c + 4], x[c + 5]);
-            mx[3] = ptx::max3(mx[3], x[c + 6], x[c + 7]);
+          for (int q2 = 0; q2 < 2; ++q2) ptx::tmem_ld32(lane_base + colS + c_base + q2 * 32, xr[q2]);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int q2 = 0; q2 < 2; ++q2) {
+            ptx::tmem_ld_acquire(xr[q2]);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) x[q2 * 32 + c] = __uint_as_float(xr[q2][c]);
           }
-          mx[0] = ptx::max3(mx[0], x[kHalf - 4], x[kHalf - 3]);
-          mx[1] = ptx::max3(mx[1], x[kHalf - 2], x[kHalf - 1]);
-          tmax = ptx::max3(mx[0], mx[1], fmaxf(mx[2], mx[3])) * c2;  // c2 > 0: scaling commutes with max
-          xs = c2;
         }
-      }
-      sh->pmax[par][half][row] = tmax;
-      ptx::named_bar_sync(1, 256);  // exchange the partial row maxima of the two halves
-      if (tid == 0) FA_TRACE(10);
-      if (ok) {
-        tmax = fmaxf(tmax, sh->pmax[par][half ^ 1][row]);
-        m_true = fmaxf(m_true, tmax);
-        const float m_cand = fmaxf(m_ref, tmax);
-        if (__any_sync(0xffffffffu, (m_cand - m_ref) > kLazyRescale)) {
-          const float alpha = ptx::ex2(m_ref - m_cand);
-          l *= alpha;
-          m_ref = m_cand;
-          if (n > 0) {
-            ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_pv[(n - 1) & 1], ((n - 1) >> 1) & 1));
-            if (!ok) fail_at = 11;
-            if (ok) {
-              ptx::tc_fence_after();
-#pragma unroll 1
-              for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
-                uint32_t r[32];
-                ptx::tmem_ld32(lane_base + kColO + c0, r);
-                ptx::tmem_wait_ld();
-                ptx::tmem_ld_acquire(r);
+        if (MK == FLEXATTN_MASK_DOCUMENT && partial) ptx::named_bar_sync(2, 256);  // kv-tile document ids visible
+        // xs: factor still to be applied to x inside the exp2 argument (the plain-score fast path keeps the raw
+        // scores and folds sm_scale*log2e into the FMA that also subtracts the running max)
+        float tmax = kMasked, xs = 1.0f;
+        if (ok) {
+          if (partial) {
+            tmax = score_half<SK, MK, true>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di,
+                                            sh->doc[par]);
+          } else if constexpr (SK != FLEXATTN_SCORE_NONE) {
+            tmax = score_half<SK, MK, false>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di,
+                                             sh->doc[par]);
+          } else {
+            float mx[4] = {x[0], x[1], x[2], x[3]};
 #pragma unroll
-                for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
-                ptx::tmem_st32(lane_base + kColO + c0, r);
+            for (int c = 4; c + 7 < kHalf; c += 8) {
+              mx[0] = ptx::max3(mx[0], x[c], x[c + 1]);
+              mx[1] = ptx::max3(mx[1], x[c + 2], x[c + 3]);
+              mx[2] = ptx::max3(mx[2], x[c + 4], x[c + 5]);
+              mx[3] = ptx::max3(mx[3], x[c + 6], x[c + 7]);
+            }
+            mx[0] = ptx::max3(mx[0], x[kHalf - 4], x[kHalf - 3]);
+            mx[1] = ptx::max3(mx[1], x[kHalf - 2], x[kHalf - 1]);
+            tmax = ptx::max3(mx[0], mx[1], fmaxf(mx[2], mx[3])) * c2;  // c2 > 0: scaling commutes with max
+            xs = c2;
+          }
+        }
+        sh->pmax[par][half][row] = tmax;
+        ptx::named_bar_sync(1, 256);  // exchange the partial row maxima of the two halves
+        if (ok) {
+          tmax = fmaxf(tmax, sh->pmax[par][half ^ 1][row]);
+          m_true = fmaxf(m_true, tmax);
+          const float m_cand = fmaxf(m_ref, tmax);
+          if (__any_sync(0xffffffffu, (m_cand - m_ref) > kLazyRescale)) {
+            const float alpha = ptx::ex2(m_ref - m_cand);
+            l *= alpha;
+            m_ref = m_cand;
+            if (n > 0) {  // O holds the sum up to the previous tile of this item: wait for that P V, then rescale
+              ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_pv[sb == 0 ? kSBufs - 1 : sb - 1], sb == 0 ? sph ^ 1u : sph));
+              if (!ok) fail_at = 11;
+              if (ok) {
+                ptx::tc_fence_after();
+#pragma unroll 1
+                for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
+                  uint32_t r[32];
+                  ptx::tmem_ld32(lane_base + kColO + c0, r);
+                  ptx::tmem_wait_ld();
+                  ptx::tmem_ld_acquire(r);
+#pragma unroll
+                  for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+                  ptx::tmem_st32(lane_base + kColO + c0, r);
+                }
+                ptx::tmem_wait_st();
               }
-              ptx::tmem_wait_st();
             }
           }
         }
-      }
-      if (tid == 0) FA_TRACE(11);
-      if (ok) {
-        float ls[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t pk[32];
-        const float nm = ptx::kRoundLog2 - m_ref;  // pre-scaled by (1 + 2^-9) for pack_bf16_trunc; compensates the truncation
+        if (ok) {
+          float ls[4] = {0.f, 0.f, 0.f, 0.f};
+          uint32_t pk[32];
+          const float nm = ptx::kRoundLog2 - m_ref;  // pre-scaled by (1 + 2^-9) for pack_bf16_trunc; compensates the truncation
 #pragma unroll
-        for (int c = 0; c < kHalf; c += 2) {
-          const float p0 = ptx::ex2(fmaf(x[c], xs, nm)), p1 = ptx::ex2(fmaf(x[c + 1], xs, nm));
-          ls[(c >> 1) & 3] += p0 + p1;
-          pk[c >> 1] = ptx::pack_bf16_trunc(p0, p1);
+          for (int c = 0; c < kHalf; c += 2) {
+            const float p0 = ptx::ex2(fmaf(x[c], xs, nm)), p1 = ptx::ex2(fmaf(x[c + 1], xs, nm));
+            ls[(c >> 1) & 3] += p0 + p1;
+            pk[c >> 1] = ptx::pack_bf16_trunc(p0, p1);
+          }
+          ptx::tmem_st32(lane_base + colS + (c_base >> 1), pk);
+          l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+          ptx::tmem_wait_st();
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(&sh->bar_p[sb]);
         }
-        ptx::tmem_st32(lane_base + colS + (c_base >> 1), pk);
-        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-        if (tid == 0) FA_TRACE(12);
-        ptx::tmem_wait_st();
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(&sh->bar_p[sb]);
-        if (tid == 0) FA_TRACE(13);
+        if (++sb == kSBufs) { sb = 0; sph ^= 1u; }
       }
-    }
 
-    if (tid == 0) FA_MARK(7);
-    if (ok && N > 0) {
-      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_pv[(N - 1) & 1], ((N - 1) >> 1) & 1));
-      if (!ok) fail_at = 12;
-    }
-    if (tid == 0) FA_MARK(8);
-    sh->lsum[half][row] = l;
-    ptx::named_bar_sync(1, 256);
-    l = sh->lsum[0][row] + sh->lsum[1][row];
-    if (ok) {
-      const float inv_l = l > 0.f ? ptx::kRoundUp / l : 0.f;  // l sums the pre-scaled probabilities
-      const size_t grow = (size_t)bh * P.seq_q + i;
-      if (N > 0) ptx::tc_fence_after();
-      __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(P.o) + grow * D;
+      // ---- item epilogue: O / l of the item, read out of tensor memory BEFORE this warpgroup writes the next
+      // item's first P (which is what lets the MMA issuer overwrite O)
+      if (ok && N > 0) {
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_pv[sb == 0 ? kSBufs - 1 : sb - 1], sb == 0 ? sph ^ 1u : sph));
+        if (!ok) fail_at = 12;
+      }
+      sh->lsum[half][row] = l;
+      ptx::named_bar_sync(1, 256);
+      l = sh->lsum[0][row] + sh->lsum[1][row];
+      ptx::named_bar_sync(3, 256);  // both halves have read lsum before the next item overwrites it
+      if (ok) {
+        const float inv_l = l > 0.f ? ptx::kRoundUp / l : 0.f;  // l sums the pre-scaled probabilities
+        const size_t grow = (size_t)bh * P.seq_q + i;
+        if (N > 0) ptx::tc_fence_after();
+        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(P.o) + grow * D;
 #pragma unroll 1
-      for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
-        uint32_t r[32];
-        if (N > 0) {
-          ptx::tmem_ld32(lane_base + kColO + c0, r);
-          ptx::tmem_wait_ld();
-          ptx::tmem_ld_acquire(r);
-        } else {
+        for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
+          uint32_t r[32];
+          if (N > 0) {
+            ptx::tmem_ld32(lane_base + kColO + c0, r);
+            ptx::tmem_wait_ld();
+            ptx::tmem_ld_acquire(r);
+          } else {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) r[c] = 0u;
-        }
-        if (i < P.seq_q) {
+            for (int c = 0; c < 32; ++c) r[c] = 0u;
+          }
+          if (i < P.seq_q) {
 #pragma unroll
-          for (int c = 0; c < 32; c += 8) {
-            uint4 v4;
-            v4.x = ptx::pack_bf16(__uint_as_float(r[c]) * inv_l, __uint_as_float(r[c + 1]) * inv_l);
-            v4.y = ptx::pack_bf16(__uint_as_float(r[c + 2]) * inv_l, __uint_as_float(r[c + 3]) * inv_l);
-            v4.z = ptx::pack_bf16(__uint_as_float(r[c + 4]) * inv_l, __uint_as_float(r[c + 5]) * inv_l);
-            v4.w = ptx::pack_bf16(__uint_as_float(r[c + 6]) * inv_l, __uint_as_float(r[c + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c0 + c) = v4;
+            for (int c = 0; c < 32; c += 8) {
+              uint4 v4;
+              v4.x = ptx::pack_bf16(__uint_as_float(r[c]) * inv_l, __uint_as_float(r[c + 1]) * inv_l);
+              v4.y = ptx::pack_bf16(__uint_as_float(r[c + 2]) * inv_l, __uint_as_float(r[c + 3]) * inv_l);
+              v4.z = ptx::pack_bf16(__uint_as_float(r[c + 4]) * inv_l, __uint_as_float(r[c + 5]) * inv_l);
+              v4.w = ptx::pack_bf16(__uint_as_float(r[c + 6]) * inv_l, __uint_as_float(r[c + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + c0 + c) = v4;
+            }
           }
         }
+        if (N > 0) ptx::tc_fence_before();
+        if (half == 0 && i < P.seq_q) {
+          P.l[grow] = l * ptx::ex2(m_ref - m_true) * ptx::kRoundInv;
+          P.m[grow] = m_true * kLn2;
+        }
       }
-      if (half == 0 && i < P.seq_q) {
-        P.l[grow] = l * ptx::ex2(m_ref - m_true) * ptx::kRoundInv;
-        P.m[grow] = m_true * kLn2;
-      }
-    } else if (lane == 0) {
-      give_up(abort_flag, P.status, 4, fail_at);
     }
-    if (tid == 0) FA_MARK(9);
+    if (!ok && lane == 0) give_up(abort_flag, P.status, 4, fail_at);
   }
 
   // ------------------------------------------------------------------ teardown
   ptx::tc_fence_before();
   __syncthreads();
-  if (tid == 0) FA_MARK(10);
   if (warp == kMmaWarp) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
   }
 }
 
+// Number of SMs of the current device (queried once per device).
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 template <int D, int SK, int MK>
 int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const CUtensorMap& tk,
                const CUtensorMap& tv, int* abort_flag) {
-  constexpr size_t need = 5 * (D / 64) * ptx::kPanelBytes + sizeof(PipeSmem) + 1024;
+  constexpr size_t need = 6 * (D / 64) * ptx::kPanelBytes + sizeof(PipeSmem) + 1024;
   // 512 TMEM columns per CTA: never let two CTAs share an SM (the second would spin in tcgen05.alloc)
   constexpr size_t smem = need > 120 * 1024 ? need : 120 * 1024;
   auto kern = fwd_pipe_sm100_kernel<D, SK, MK>;
@@ -442,7 +536,11 @@ int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const
       return FLEXATTN_ERR_CUDA;
     attr_set = true;
   }
-  dim3 grid(d.n_qt, d.batch * d.heads);
+  // persistent: one CTA per SM (fewer when there are fewer work items)
+  const long long items = (long long)d.n_qt * d.batch * d.heads;
+  const int sms = sm_count();
+  if (sms <= 0) return FLEXATTN_ERR_CUDA;
+  dim3 grid((unsigned)(items < sms ? items : sms));
   kern<<<grid, kThreads, smem, st>>>(tq, tk, tv, d, abort_flag);
   return cudaGetLastError() == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;
 }
