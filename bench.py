@@ -44,7 +44,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel on the c2 workload, from
 # the ncu capture summarised under profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES = {"c2": {"fwd": 253.9e6, "dq": 325.9e6, "dkv": 378.6e6}}
+NCU_TRAFFIC_BYTES = {"c2": {"fwd": 259.6e6, "dq": 325.1e6, "dkv": 377.6e6}}
 
 
 def measured_peaks():
@@ -262,7 +262,8 @@ def cpu_reference_sample(w, budget_s=15.0, max_slices=None):
         if ctx is not None:
             ctx.__exit__(None, None, None)
     flops = 14.0 * D * pairs * n
-    sample = f"{n} of {w['B'] * w['H']} (batch, head) slices of the workload, fwd+bwd, {t:.1f} s on {cores} threads"
+    sample = (f"{n} independent (batch, head) slices of the workload's shape (the workload has {w['B'] * w['H']}), "
+              f"fwd+bwd, {t:.1f} s on {cores} threads")
     return flops / t / 1e12, cores, sample, t / n
 
 
