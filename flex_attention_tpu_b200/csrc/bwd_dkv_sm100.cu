@@ -75,6 +75,19 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
                                              const int32_t* __restrict__ s_doc, int i_first, int j, int dj, int seq_q,
                                              int window, int stride, float c2, float slope2, float abase, float capl2,
                                              float csc) {
+  if constexpr (SK == FLEXATTN_SCORE_NONE && !kPartial) {
+    // plain scores, no masked element: two columns per instruction (packed f32x2)
+    const uint64_t c22 = ptx::pack2(c2, c2);
+#pragma unroll
+    for (int c = 0; c < 32; c += 2) {
+      float a0, a1;
+      ptx::unpack2(ptx::fma2(ptx::pack2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), c22, ptx::pack2(nl[c], nl[c + 1])), a0, a1);
+      const float p0 = ptx::ex2(a0), p1 = ptx::ex2(a1);
+      s[c] = __float_as_uint(p0);
+      s[c + 1] = __float_as_uint(p1);
+      pk_p[c >> 1] = ptx::pack_bf16_trunc(p0, p1);
+    }
+  } else {
 #pragma unroll
   for (int c = 0; c < 32; c += 2) {
     float pv[2];
@@ -105,15 +118,18 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
     }
     pk_p[c >> 1] = ptx::pack_bf16_trunc(pv[0], pv[1]);
   }
+  }
 }
 
 // Second phase, 32 columns: dS^T = (p dsigma) * (dP^T - delta), packed bf16.
 __device__ __forceinline__ void dkv_ds_math32(const uint32_t (&pd)[32], const uint32_t (&pr)[32],
                                               uint32_t* __restrict__ pk_ds, const float (&dl)[32]) {
 #pragma unroll
-  for (int c = 0; c < 32; c += 2) {
-    const float d0 = __uint_as_float(pd[c]) * (__uint_as_float(pr[c]) - dl[c]);
-    const float d1 = __uint_as_float(pd[c + 1]) * (__uint_as_float(pr[c + 1]) - dl[c + 1]);
+  for (int c = 0; c < 32; c += 2) {  // two columns per instruction (packed f32x2)
+    float d0, d1;
+    const uint64_t pd2 = ptx::pack2(__uint_as_float(pd[c]), __uint_as_float(pd[c + 1]));
+    const uint64_t pr2 = ptx::pack2(__uint_as_float(pr[c]), __uint_as_float(pr[c + 1]));
+    ptx::unpack2(ptx::mul2(pd2, ptx::sub2(pr2, ptx::pack2(dl[c], dl[c + 1]))), d0, d1);
     pk_ds[c >> 1] = ptx::pack_bf16_trunc(d0, d1);
   }
 }

@@ -49,6 +49,19 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
                                              int window, int stride, float c2, float slope2, float abase, float capl2,
                                              float csc) {
   const float bias0 = abase + nlse2;  // ALiBi: slope * (j_first - i), folded with the row's -lse2
+  if constexpr (SK == FLEXATTN_SCORE_NONE && !kPartial) {
+    // plain scores, no masked element: two columns per instruction (packed f32x2)
+    const uint64_t c22 = ptx::pack2(c2, c2), nl2 = ptx::pack2(nlse2, nlse2), dl2 = ptx::pack2(delta, delta);
+#pragma unroll
+    for (int c = 0; c < 64; c += 2) {
+      float a0, a1, d0, d1;
+      ptx::unpack2(ptx::fma2(ptx::pack2(__uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1])), c22, nl2), a0, a1);
+      const uint64_t p2 = ptx::pack2(ptx::ex2(a0), ptx::ex2(a1));
+      const uint64_t dp2 = ptx::pack2(__uint_as_float(pr[c >> 5][c & 31]), __uint_as_float(pr[c >> 5][(c & 31) + 1]));
+      ptx::unpack2(ptx::mul2(p2, ptx::sub2(dp2, dl2)), d0, d1);
+      pk[c >> 1] = ptx::pack_bf16_trunc(d0, d1);
+    }
+  } else {
 #pragma unroll
   for (int c = 0; c < 64; c += 2) {
     float dv[2];
@@ -79,6 +92,7 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
       dv[u] = d;
     }
     pk[c >> 1] = ptx::pack_bf16_trunc(dv[0], dv[1]);
+  }
   }
 }
 

@@ -435,17 +435,24 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         if (ok) {
-          float ls[4] = {0.f, 0.f, 0.f, 0.f};
+          uint64_t ls2[2] = {0ull, 0ull};  // packed partial sums (four running sums in two registers pairs)
           uint32_t pk[32];
           const float nm = ptx::kRoundLog2 - m_ref;  // pre-scaled by (1 + 2^-9) for pack_bf16_trunc; compensates the truncation
+          const uint64_t xs2 = ptx::pack2(xs, xs), nm2 = ptx::pack2(nm, nm);
 #pragma unroll
           for (int c = 0; c < kHalf; c += 2) {
-            const float p0 = ptx::ex2(fmaf(x[c], xs, nm)), p1 = ptx::ex2(fmaf(x[c + 1], xs, nm));
-            ls[(c >> 1) & 3] += p0 + p1;
+            float a0, a1;
+            ptx::unpack2(ptx::fma2(ptx::pack2(x[c], x[c + 1]), xs2, nm2), a0, a1);
+            const float p0 = ptx::ex2(a0), p1 = ptx::ex2(a1);
+            ls2[(c >> 1) & 1] = ptx::add2(ls2[(c >> 1) & 1], ptx::pack2(p0, p1));
             pk[c >> 1] = ptx::pack_bf16_trunc(p0, p1);
           }
           ptx::tmem_st32(lane_base + colS + (c_base >> 1), pk);
-          l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+          {
+            float s0, s1;
+            ptx::unpack2(ptx::add2(ls2[0], ls2[1]), s0, s1);
+            l += s0 + s1;
+          }
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           ptx::mbar_arrive(&sh->bar_p[sb]);
