@@ -75,49 +75,61 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
                                              const int32_t* __restrict__ s_doc, int i_first, int j, int dj, int seq_q,
                                              int window, int stride, float c2, float slope2, float abase, float capl2,
                                              float csc) {
-  if constexpr (SK == FLEXATTN_SCORE_NONE && !kPartial) {
-    // plain scores, no masked element: two columns per instruction (packed f32x2)
-    const uint64_t c22 = ptx::pack2(c2, c2);
+  if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+    // scalar form: the packed one costs registers here (tanh, its derivative and the mask live together)
 #pragma unroll
     for (int c = 0; c < 32; c += 2) {
-      float a0, a1;
-      ptx::unpack2(ptx::fma2(ptx::pack2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), c22, ptx::pack2(nl[c], nl[c + 1])), a0, a1);
-      const float p0 = ptx::ex2(a0), p1 = ptx::ex2(a1);
-      s[c] = __float_as_uint(p0);
-      s[c + 1] = __float_as_uint(p1);
-      pk_p[c >> 1] = ptx::pack_bf16_trunc(p0, p1);
+      float pv[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int cc = c + u;
+        const float th = ptx::tanh_approx(__uint_as_float(s[cc]) * csc);
+        float p = ptx::ex2(fmaf(capl2, th, nl[cc]));
+        if constexpr (kPartial) {
+          const int i = i_first + cc;
+          const int di = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[cc] : 0;
+          p = ((i < seq_q) && mask_keep<MK>(i, j, window, stride, di, dj)) ? p : 0.f;
+        }
+        pv[u] = p;
+        s[cc] = __float_as_uint(p * fmaf(-th, th, 1.f));
+      }
+      pk_p[c >> 1] = ptx::pack_bf16_trunc(pv[0], pv[1]);
     }
-  } else {
+    return;
+  }
+  // two columns per instruction (packed f32x2) wherever the arithmetic allows it
+  const uint64_t c22 = ptx::pack2(c2, c2);
 #pragma unroll
   for (int c = 0; c < 32; c += 2) {
-    float pv[2];
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int cc = c + u;
-      const float sv = __uint_as_float(s[cc]);
-      float arg, dsig = 1.f;  // arg = log2-domain logit minus the row's log-sum-exp
-      if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
-        arg = fmaf(sv, c2, fmaf(-slope2, (float)cc, abase) + nl[cc]);
-      } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
-        const float th = ptx::tanh_approx(sv * csc);
-        arg = fmaf(capl2, th, nl[cc]);
-        dsig = fmaf(-th, th, 1.f);
-      } else {
-        arg = fmaf(sv, c2, nl[cc]);
-      }
-      float p = ptx::ex2(arg);
-      if constexpr (kPartial) {
-        const int i = i_first + cc;
-        const int di = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[cc] : 0;
-        const bool keep = (i < seq_q) && mask_keep<MK>(i, j, window, stride, di, dj);
-        p = keep ? p : 0.f;
-      }
-      pv[u] = p;
-      if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) p *= dsig;
-      s[cc] = __float_as_uint(p);
+    const uint64_t sv2 = ptx::pack2(__uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+    const uint64_t nl2 = ptx::pack2(nl[c], nl[c + 1]);
+    uint64_t arg2, dsig2 = 0;  // arg = log2-domain logit minus the row's log-sum-exp
+    if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
+      // bias = abase - slope2 * column: the column part is a compile-time pair
+      const uint64_t b2 = ptx::fma2(ptx::pack2(-(float)c, -(float)(c + 1)), ptx::pack2(slope2, slope2), ptx::pack2(abase, abase));
+      arg2 = ptx::fma2(sv2, c22, ptx::add2(b2, nl2));
+    } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+      float t0, t1;
+      ptx::unpack2(ptx::mul2(sv2, ptx::pack2(csc, csc)), t0, t1);
+      const uint64_t th2 = ptx::pack2(ptx::tanh_approx(t0), ptx::tanh_approx(t1));
+      arg2 = ptx::fma2(ptx::pack2(capl2, capl2), th2, nl2);
+      dsig2 = ptx::fma2(ptx::sub2(0ull, th2), th2, ptx::pack2(1.f, 1.f));
+    } else {
+      arg2 = ptx::fma2(sv2, c22, nl2);
     }
-    pk_p[c >> 1] = ptx::pack_bf16_trunc(pv[0], pv[1]);
-  }
+    float a0, a1;
+    ptx::unpack2(arg2, a0, a1);
+    float p0 = ptx::ex2(a0), p1 = ptx::ex2(a1);
+    if constexpr (kPartial) {
+      const int i = i_first + c;
+      const int d0 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c] : 0, d1 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c + 1] : 0;
+      p0 = ((i < seq_q) && mask_keep<MK>(i, j, window, stride, d0, dj)) ? p0 : 0.f;
+      p1 = ((i + 1 < seq_q) && mask_keep<MK>(i + 1, j, window, stride, d1, dj)) ? p1 : 0.f;
+    }
+    pk_p[c >> 1] = ptx::pack_bf16_trunc(p0, p1);
+    if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) ptx::unpack2(ptx::mul2(ptx::pack2(p0, p1), dsig2), p0, p1);
+    s[c] = __float_as_uint(p0);
+    s[c + 1] = __float_as_uint(p1);
   }
 }
 

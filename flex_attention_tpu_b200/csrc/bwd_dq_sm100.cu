@@ -49,50 +49,60 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
                                              int window, int stride, float c2, float slope2, float abase, float capl2,
                                              float csc) {
   const float bias0 = abase + nlse2;  // ALiBi: slope * (j_first - i), folded with the row's -lse2
-  if constexpr (SK == FLEXATTN_SCORE_NONE && !kPartial) {
-    // plain scores, no masked element: two columns per instruction (packed f32x2)
-    const uint64_t c22 = ptx::pack2(c2, c2), nl2 = ptx::pack2(nlse2, nlse2), dl2 = ptx::pack2(delta, delta);
+  if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+    // scalar form: the packed one costs registers here (tanh, its derivative and the mask live together)
 #pragma unroll
     for (int c = 0; c < 64; c += 2) {
-      float a0, a1, d0, d1;
-      ptx::unpack2(ptx::fma2(ptx::pack2(__uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1])), c22, nl2), a0, a1);
-      const uint64_t p2 = ptx::pack2(ptx::ex2(a0), ptx::ex2(a1));
-      const uint64_t dp2 = ptx::pack2(__uint_as_float(pr[c >> 5][c & 31]), __uint_as_float(pr[c >> 5][(c & 31) + 1]));
-      ptx::unpack2(ptx::mul2(p2, ptx::sub2(dp2, dl2)), d0, d1);
-      pk[c >> 1] = ptx::pack_bf16_trunc(d0, d1);
+      float dv[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int cc = c + u;
+        const float th = ptx::tanh_approx(__uint_as_float(sr[cc >> 5][cc & 31]) * csc);
+        float p = ptx::ex2(fmaf(capl2, th, nlse2));
+        if constexpr (kPartial) {
+          const int j = j_first + cc;
+          const int dj = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[cc] : 0;
+          p = ((j < seq_k) && mask_keep<MK>(i, j, window, stride, di, dj)) ? p : 0.f;
+        }
+        dv[u] = p * (__uint_as_float(pr[cc >> 5][cc & 31]) - delta) * fmaf(-th, th, 1.f);
+      }
+      pk[c >> 1] = ptx::pack_bf16_trunc(dv[0], dv[1]);
     }
-  } else {
+    return;
+  }
+  // two columns per instruction (packed f32x2) wherever the arithmetic allows it
+  const uint64_t c22 = ptx::pack2(c2, c2), nl2 = ptx::pack2(nlse2, nlse2), dl2 = ptx::pack2(delta, delta);
 #pragma unroll
   for (int c = 0; c < 64; c += 2) {
-    float dv[2];
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int cc = c + u;
-      const float s = __uint_as_float(sr[cc >> 5][cc & 31]);
-      const float dp = __uint_as_float(pr[cc >> 5][cc & 31]);
-      float arg, dsig = 1.f;
-      if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
-        arg = fmaf(s, c2, fmaf(slope2, (float)cc, bias0));
-      } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
-        const float th = ptx::tanh_approx(s * csc);
-        arg = fmaf(capl2, th, nlse2);
-        dsig = fmaf(-th, th, 1.f);
-      } else {
-        arg = fmaf(s, c2, nlse2);
-      }
-      float p = ptx::ex2(arg);
-      if constexpr (kPartial) {
-        const int j = j_first + cc;
-        const int dj = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[cc] : 0;
-        const bool keep = (j < seq_k) && mask_keep<MK>(i, j, window, stride, di, dj);
-        p = keep ? p : 0.f;
-      }
-      float d = p * (dp - delta);
-      if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) d *= dsig;
-      dv[u] = d;
+    const uint64_t s2 = ptx::pack2(__uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1]));
+    const uint64_t dp2 = ptx::pack2(__uint_as_float(pr[c >> 5][c & 31]), __uint_as_float(pr[c >> 5][(c & 31) + 1]));
+    uint64_t arg2, dsig2 = 0;
+    if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
+      const uint64_t b2 = ptx::fma2(ptx::pack2((float)c, (float)(c + 1)), ptx::pack2(slope2, slope2), ptx::pack2(bias0, bias0));
+      arg2 = ptx::fma2(s2, c22, b2);
+    } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+      float t0, t1;
+      ptx::unpack2(ptx::mul2(s2, ptx::pack2(csc, csc)), t0, t1);
+      const uint64_t th2 = ptx::pack2(ptx::tanh_approx(t0), ptx::tanh_approx(t1));
+      arg2 = ptx::fma2(ptx::pack2(capl2, capl2), th2, nl2);
+      dsig2 = ptx::fma2(ptx::sub2(0ull, th2), th2, ptx::pack2(1.f, 1.f));
+    } else {
+      arg2 = ptx::fma2(s2, c22, nl2);
     }
-    pk[c >> 1] = ptx::pack_bf16_trunc(dv[0], dv[1]);
-  }
+    float a0, a1;
+    ptx::unpack2(arg2, a0, a1);
+    float p0 = ptx::ex2(a0), p1 = ptx::ex2(a1);
+    if constexpr (kPartial) {
+      const int j = j_first + c;
+      const int d0 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c] : 0, d1 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c + 1] : 0;
+      p0 = ((j < seq_k) && mask_keep<MK>(i, j, window, stride, di, d0)) ? p0 : 0.f;
+      p1 = ((j + 1 < seq_k) && mask_keep<MK>(i, j + 1, window, stride, di, d1)) ? p1 : 0.f;
+    }
+    uint64_t d2 = ptx::mul2(ptx::pack2(p0, p1), ptx::sub2(dp2, dl2));
+    if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) d2 = ptx::mul2(d2, dsig2);
+    float d0f, d1f;
+    ptx::unpack2(d2, d0f, d1f);
+    pk[c >> 1] = ptx::pack_bf16_trunc(d0f, d1f);
   }
 }
 

@@ -114,26 +114,45 @@ __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, in
                                             const int32_t* s_doc) {
   float mx[4] = {kMasked, kMasked, kMasked, kMasked};
   const float abase = slope2 * (float)(j0 + c_base - i);
+  if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+    // scalar form: the packed one costs registers here
 #pragma unroll
-  for (int c = 0; c < kHalf; ++c) {
-    float t;
+    for (int c = 0; c < kHalf; ++c) {
+      float t = capl2 * ptx::tanh_approx(x[c] * csc);
+      if constexpr (kPartial) {
+        const int j = j0 + c_base + c;
+        const int dj = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c_base + c] : 0;
+        t = ((j < seq_k) && mask_keep<MK>(i, j, window, stride, di, dj)) ? t : kMasked;
+      }
+      x[c] = t;
+      mx[c & 3] = fmaxf(mx[c & 3], t);
+    }
+    return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+  } else {
+  // the score arithmetic runs two columns per instruction (packed f32x2); masking and the maximum are scalar
+#pragma unroll
+  for (int c = 0; c < kHalf; c += 2) {
+    const uint64_t x2 = ptx::pack2(x[c], x[c + 1]);
+    float t0, t1;
     if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
-      t = fmaf(x[c], c2, fmaf(slope2, (float)c, abase));
-    } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
-      t = capl2 * ptx::tanh_approx(x[c] * csc);
+      const uint64_t b2 = ptx::fma2(ptx::pack2((float)c, (float)(c + 1)), ptx::pack2(slope2, slope2), ptx::pack2(abase, abase));
+      ptx::unpack2(ptx::fma2(x2, ptx::pack2(c2, c2), b2), t0, t1);
     } else {
-      t = x[c] * c2;
+      ptx::unpack2(ptx::mul2(x2, ptx::pack2(c2, c2)), t0, t1);
     }
     if constexpr (kPartial) {
       const int j = j0 + c_base + c;
-      const int dj = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c_base + c] : 0;
-      const bool keep = (j < seq_k) && mask_keep<MK>(i, j, window, stride, di, dj);
-      t = keep ? t : kMasked;
+      const int d0 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c_base + c] : 0;
+      const int d1 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c_base + c + 1] : 0;
+      t0 = ((j < seq_k) && mask_keep<MK>(i, j, window, stride, di, d0)) ? t0 : kMasked;
+      t1 = ((j + 1 < seq_k) && mask_keep<MK>(i, j + 1, window, stride, di, d1)) ? t1 : kMasked;
     }
-    x[c] = t;
-    mx[c & 3] = fmaxf(mx[c & 3], t);
+    x[c] = t0;
+    x[c + 1] = t1;
+    mx[(c >> 1) & 3] = ptx::max3(mx[(c >> 1) & 3], t0, t1);
   }
   return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+  }
 }
 
 template <int D, int SK, int MK>
