@@ -150,6 +150,7 @@ template <int D, int SK, int MK>
 __global__ void __launch_bounds__(kThreads, 1)
     dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                     const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                      const DevParams P, int* abort_flag) {
   constexpr int kPanels = D / 64;
   constexpr uint32_t kTileBytes = kPanels * ptx::kPanelBytes;
@@ -456,41 +457,49 @@ __global__ void __launch_bounds__(kThreads, 1)
       ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_acc, 0));  // every accumulation MMA has completed
       if (!ok) fail_at = 12;
     }
+    // Epilogue: warpgroup 0 stores dK * sm_scale, warpgroup 1 dV: bf16 into a shared-memory tile in the TMA
+    // (128-byte swizzle) layout, then one bulk tensor store per 64-column panel.  The Q / dO rings are free by now
+    // (every MMA has completed); rows past seq_k are clipped by the tensor map.
+    uint8_t* stage = half ? sDO : sQ;
     if (ok) {
       if (N > 0) ptx::tc_fence_after();
-      const size_t grow = (size_t)bh * P.seq_k + j;
-      {
-        const int which = half;  // warpgroup 0 stores dK, warpgroup 1 stores dV
-        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(which ? P.dv : P.dk) + grow * D;
-        const float sc = which ? 1.f : P.sm_scale;
-        const uint32_t col = which ? kColDV : kColDK;
+      const float sc = half ? 1.f : P.sm_scale;
+      const uint32_t col0 = half ? kColDV : kColDK;
+      uint8_t* stage_row = stage + row * 128;
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t r[32];
-          if (N > 0) {
-            ptx::tmem_ld32(lane_base + col + c0, r);
-            ptx::tmem_wait_ld();
-            ptx::tmem_ld_acquire(r);
-          } else {
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t r[32];
+        if (N > 0) {
+          ptx::tmem_ld32(lane_base + col0 + c0, r);
+          ptx::tmem_wait_ld();
+          ptx::tmem_ld_acquire(r);
+        } else {
 #pragma unroll
-            for (int c = 0; c < 32; ++c) r[c] = 0u;
-          }
-          if (row_ok) {
+          for (int c = 0; c < 32; ++c) r[c] = 0u;
+        }
 #pragma unroll
-            for (int c = 0; c < 32; c += 8) {
-              uint4 v4;
-              v4.x = ptx::pack_bf16(__uint_as_float(r[c]) * sc, __uint_as_float(r[c + 1]) * sc);
-              v4.y = ptx::pack_bf16(__uint_as_float(r[c + 2]) * sc, __uint_as_float(r[c + 3]) * sc);
-              v4.z = ptx::pack_bf16(__uint_as_float(r[c + 4]) * sc, __uint_as_float(r[c + 5]) * sc);
-              v4.w = ptx::pack_bf16(__uint_as_float(r[c + 6]) * sc, __uint_as_float(r[c + 7]) * sc);
-              *reinterpret_cast<uint4*>(out + c0 + c) = v4;
-            }
-          }
+        for (int c = 0; c < 32; c += 8) {
+          uint4 v4;
+          v4.x = ptx::pack_bf16(__uint_as_float(r[c]) * sc, __uint_as_float(r[c + 1]) * sc);
+          v4.y = ptx::pack_bf16(__uint_as_float(r[c + 2]) * sc, __uint_as_float(r[c + 3]) * sc);
+          v4.z = ptx::pack_bf16(__uint_as_float(r[c + 4]) * sc, __uint_as_float(r[c + 5]) * sc);
+          v4.w = ptx::pack_bf16(__uint_as_float(r[c + 6]) * sc, __uint_as_float(r[c + 7]) * sc);
+          const int col = c0 + c, panel = col >> 6, chunk = (col & 63) >> 3;
+          *reinterpret_cast<uint4*>(stage_row + panel * ptx::kPanelBytes + ((chunk ^ (row & 7)) << 4)) = v4;
         }
       }
-    } else if (lane == 0) {
-      give_up(abort_flag, P.status, 3, fail_at);
+      ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the bulk store
     }
+    ptx::named_bar_sync(1 + half, 128);
+    if (ok && row == 0) {
+#pragma unroll
+      for (int p = 0; p < kPanels; ++p)
+        ptx::tma_store_3d(half ? &tm_dv : &tm_dk, stage + p * ptx::kPanelBytes, p * 64, kt * kTile, bh);
+      ptx::tma_store_commit();
+      ptx::tma_store_wait_read();  // shared memory must stay intact until the store has read it
+    }
+    if (!ok && lane == 0) give_up(abort_flag, P.status, 3, fail_at);
+
   }
 
   ptx::tc_fence_before();
@@ -503,7 +512,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 template <int D, int SK, int MK>
 int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const CUtensorMap& tdo,
-               const CUtensorMap& tk, const CUtensorMap& tv, int* abort_flag) {
+               const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdk, const CUtensorMap& tdv,
+               int* abort_flag) {
   constexpr size_t smem = 6 * (D / 64) * ptx::kPanelBytes + sizeof(DkvSmem) + 1024;
   // 512 TMEM columns per CTA: never let two CTAs share an SM (the second would spin in tcgen05.alloc)
   constexpr size_t smem_req = smem > 120 * 1024 ? smem : 120 * 1024;
@@ -515,32 +525,32 @@ int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const
     attr_set = true;
   }
   dim3 grid(d.n_kt, d.batch * d.heads);
-  kern<<<grid, kThreads, smem_req, st>>>(tq, tdo, tk, tv, d, abort_flag);
+  kern<<<grid, kThreads, smem_req, st>>>(tq, tdo, tk, tv, tdk, tdv, d, abort_flag);
   return cudaGetLastError() == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;
 }
 
 template <int D, int SK>
 int launch_mask(cudaStream_t st, const DevParams& d, int mask, const CUtensorMap& tq, const CUtensorMap& tdo,
-                const CUtensorMap& tk, const CUtensorMap& tv, int* af) {
+                const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdk, const CUtensorMap& tdv, int* af) {
   switch (mask) {
-    case FLEXATTN_MASK_NONE: return launch_one<D, SK, FLEXATTN_MASK_NONE>(st, d, tq, tdo, tk, tv, af);
-    case FLEXATTN_MASK_CAUSAL: return launch_one<D, SK, FLEXATTN_MASK_CAUSAL>(st, d, tq, tdo, tk, tv, af);
-    case FLEXATTN_MASK_SLIDING_WINDOW: return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW>(st, d, tq, tdo, tk, tv, af);
+    case FLEXATTN_MASK_NONE: return launch_one<D, SK, FLEXATTN_MASK_NONE>(st, d, tq, tdo, tk, tv, tdk, tdv, af);
+    case FLEXATTN_MASK_CAUSAL: return launch_one<D, SK, FLEXATTN_MASK_CAUSAL>(st, d, tq, tdo, tk, tv, tdk, tdv, af);
+    case FLEXATTN_MASK_SLIDING_WINDOW: return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW>(st, d, tq, tdo, tk, tv, tdk, tdv, af);
     case FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL:
-      return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL>(st, d, tq, tdo, tk, tv, af);
-    case FLEXATTN_MASK_DOCUMENT: return launch_one<D, SK, FLEXATTN_MASK_DOCUMENT>(st, d, tq, tdo, tk, tv, af);
-    case FLEXATTN_MASK_S2: return launch_one<D, SK, FLEXATTN_MASK_S2>(st, d, tq, tdo, tk, tv, af);
+      return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL>(st, d, tq, tdo, tk, tv, tdk, tdv, af);
+    case FLEXATTN_MASK_DOCUMENT: return launch_one<D, SK, FLEXATTN_MASK_DOCUMENT>(st, d, tq, tdo, tk, tv, tdk, tdv, af);
+    case FLEXATTN_MASK_S2: return launch_one<D, SK, FLEXATTN_MASK_S2>(st, d, tq, tdo, tk, tv, tdk, tdv, af);
     default: return FLEXATTN_ERR_UNSUPPORTED_MOD;
   }
 }
 
 template <int D>
 int launch_score(cudaStream_t st, const DevParams& d, int score, int mask, const CUtensorMap& tq,
-                 const CUtensorMap& tdo, const CUtensorMap& tk, const CUtensorMap& tv, int* af) {
+                 const CUtensorMap& tdo, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdk, const CUtensorMap& tdv, int* af) {
   switch (score) {
-    case FLEXATTN_SCORE_NONE: return launch_mask<D, FLEXATTN_SCORE_NONE>(st, d, mask, tq, tdo, tk, tv, af);
-    case FLEXATTN_SCORE_ALIBI: return launch_mask<D, FLEXATTN_SCORE_ALIBI>(st, d, mask, tq, tdo, tk, tv, af);
-    case FLEXATTN_SCORE_SOFTCAP: return launch_mask<D, FLEXATTN_SCORE_SOFTCAP>(st, d, mask, tq, tdo, tk, tv, af);
+    case FLEXATTN_SCORE_NONE: return launch_mask<D, FLEXATTN_SCORE_NONE>(st, d, mask, tq, tdo, tk, tv, tdk, tdv, af);
+    case FLEXATTN_SCORE_ALIBI: return launch_mask<D, FLEXATTN_SCORE_ALIBI>(st, d, mask, tq, tdo, tk, tv, tdk, tdv, af);
+    case FLEXATTN_SCORE_SOFTCAP: return launch_mask<D, FLEXATTN_SCORE_SOFTCAP>(st, d, mask, tq, tdo, tk, tv, tdk, tdv, af);
     default: return FLEXATTN_ERR_UNSUPPORTED_MOD;
   }
 }
@@ -550,7 +560,7 @@ int launch_score(cudaStream_t st, const DevParams& d, int score, int mask, const
 int launch_sm100_dkv(cudaStream_t st, const DevParams& d, int score, int mask) {
   int* af = abort_flag_ptr();
   if (af == nullptr) return FLEXATTN_ERR_CUDA;
-  CUtensorMap tq, tdo, tk, tv;
+  CUtensorMap tq, tdo, tk, tv, tdk, tdv;
   const int slices = d.batch * d.heads;
   int e = make_tile_map(&tq, d.q, slices, d.seq_q, d.head_dim);
   if (e) return e;
@@ -560,8 +570,12 @@ int launch_sm100_dkv(cudaStream_t st, const DevParams& d, int score, int mask) {
   if (e) return e;
   e = make_tile_map(&tv, d.v, slices, d.seq_k, d.head_dim);
   if (e) return e;
-  if (d.head_dim == 128) return launch_score<128>(st, d, score, mask, tq, tdo, tk, tv, af);
-  if (d.head_dim == 64) return launch_score<64>(st, d, score, mask, tq, tdo, tk, tv, af);
+  e = make_tile_map(&tdk, d.dk, slices, d.seq_k, d.head_dim);
+  if (e) return e;
+  e = make_tile_map(&tdv, d.dv, slices, d.seq_k, d.head_dim);
+  if (e) return e;
+  if (d.head_dim == 128) return launch_score<128>(st, d, score, mask, tq, tdo, tk, tv, tdk, tdv, af);
+  if (d.head_dim == 64) return launch_score<64>(st, d, score, mask, tq, tdo, tk, tv, tdk, tdv, af);
   return FLEXATTN_ERR_UNSUPPORTED_HEAD_DIM;
 }
 

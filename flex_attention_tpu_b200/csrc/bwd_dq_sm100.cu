@@ -23,8 +23,14 @@
     if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64)     \
       P.trace[n * 16 + (slot)] = clock64();                                     \
   } while (0)
+#define FA_MARK(slot)                                                           \
+  do {                                                                          \
+    if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) \
+      P.trace[63 * 16 + (slot)] = clock64();                                    \
+  } while (0)
 #else
 #define FA_TRACE(slot)
+#define FA_MARK(slot)
 #endif
 
 namespace flexattn {
@@ -110,7 +116,7 @@ template <int D, int SK, int MK>
 __global__ void __launch_bounds__(kThreads, 1)
     dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                    const DevParams P, int* abort_flag) {
+                    const __grid_constant__ CUtensorMap tm_dq, const DevParams P, int* abort_flag) {
   constexpr int kPanels = D / 64;
   constexpr uint32_t kTileBytes = kPanels * ptx::kPanelBytes;
   constexpr uint32_t kDsBytes = 2 * ptx::kPanelBytes;  // dS tile: 128 query rows x 128 keys, bf16
@@ -134,6 +140,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int4 rm = P.row_map[(size_t)(P.map_rows > 1 ? b : 0) * P.n_qt + qt];
   const int N = rm.y - rm.x;
 
+  FA_MARK(0);
   if (*reinterpret_cast<volatile int*>(abort_flag) != 0) return;
 
   if (tid == 0) {
@@ -156,6 +163,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
+  FA_MARK(1);
 
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
@@ -277,6 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // half) moves the 64 elements of 128-byte panel `half`: chunk j of the row sits at slot j ^ (row & 7).
     if (N > 0) {
       ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_q, 0));
+      FA_MARK(2);
       if (!ok) fail_at = 9;
       if (ok) {
         if constexpr (D == 128) {
@@ -305,6 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::tc_fence_before();
       }
       ptx::mbar_arrive(&sh->bar_qtm);
+      FA_MARK(3);
     }
 
     for (int n = 0; n < N; ++n) {
@@ -324,6 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!ok) continue;
       if (tid == 0) FA_TRACE(8);
+      if (n == 0) FA_MARK(4);
       ptx::tc_fence_after();
       uint32_t sr[2][32], pr[2][32];
       ptx::tmem_ld32(lane_base + kColS + half * 64, sr[0]);
@@ -361,14 +372,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (tid == 0) FA_TRACE(11);
     }
 
+    FA_MARK(5);
     if (ok && N > 0) {
       ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dq, (N - 1) & 1));
       if (!ok) fail_at = 12;
     }
+    FA_MARK(6);
+    // Epilogue: dQ * sm_scale as bf16 into a shared-memory tile in the TMA (128-byte swizzle) layout, then one
+    // bulk tensor store per 64-column panel.  The K/V ring is free by now (every MMA has completed); rows past
+    // seq_q are clipped by the tensor map.
     if (ok) {
       if (N > 0) ptx::tc_fence_after();
-      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(P.dq) + grow * D;
       const float sc = P.sm_scale;
+      uint8_t* stage_row = sKV + row * 128;
 #pragma unroll 1
       for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
         uint32_t r[32];
@@ -380,25 +396,34 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int c = 0; c < 32; ++c) r[c] = 0u;
         }
-        if (row_ok) {
 #pragma unroll
-          for (int c = 0; c < 32; c += 8) {
-            uint4 v4;
-            v4.x = ptx::pack_bf16(__uint_as_float(r[c]) * sc, __uint_as_float(r[c + 1]) * sc);
-            v4.y = ptx::pack_bf16(__uint_as_float(r[c + 2]) * sc, __uint_as_float(r[c + 3]) * sc);
-            v4.z = ptx::pack_bf16(__uint_as_float(r[c + 4]) * sc, __uint_as_float(r[c + 5]) * sc);
-            v4.w = ptx::pack_bf16(__uint_as_float(r[c + 6]) * sc, __uint_as_float(r[c + 7]) * sc);
-            *reinterpret_cast<uint4*>(out + c0 + c) = v4;
-          }
+        for (int c = 0; c < 32; c += 8) {
+          uint4 v4;
+          v4.x = ptx::pack_bf16(__uint_as_float(r[c]) * sc, __uint_as_float(r[c + 1]) * sc);
+          v4.y = ptx::pack_bf16(__uint_as_float(r[c + 2]) * sc, __uint_as_float(r[c + 3]) * sc);
+          v4.z = ptx::pack_bf16(__uint_as_float(r[c + 4]) * sc, __uint_as_float(r[c + 5]) * sc);
+          v4.w = ptx::pack_bf16(__uint_as_float(r[c + 6]) * sc, __uint_as_float(r[c + 7]) * sc);
+          const int col = c0 + c, panel = col >> 6, chunk = (col & 63) >> 3;
+          *reinterpret_cast<uint4*>(stage_row + panel * ptx::kPanelBytes + ((chunk ^ (row & 7)) << 4)) = v4;
         }
       }
-    } else if (lane == 0) {
-      give_up(abort_flag, P.status, 2, fail_at);
+      ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the bulk store
     }
+    ptx::named_bar_sync(3, 256);
+    if (ok && tid == 0) {
+#pragma unroll
+      for (int p = 0; p < kPanels; ++p) ptx::tma_store_3d(&tm_dq, sKV + p * ptx::kPanelBytes, p * 64, qt * kTile, bh);
+      ptx::tma_store_commit();
+      ptx::tma_store_wait_read();  // shared memory must stay intact until the store has read it
+    }
+    if (!ok && lane == 0) give_up(abort_flag, P.status, 2, fail_at);
+
+    FA_MARK(7);
   }
 
   ptx::tc_fence_before();
   __syncthreads();
+  FA_MARK(8);
   if (warp == kMmaWarp) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
@@ -407,7 +432,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 template <int D, int SK, int MK>
 int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const CUtensorMap& tdo,
-               const CUtensorMap& tk, const CUtensorMap& tv, int* abort_flag) {
+               const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdq, int* abort_flag) {
   constexpr size_t smem = 6 * (D / 64) * ptx::kPanelBytes + 2 * ptx::kPanelBytes + sizeof(DqSmem) + 1024;
   // 512 TMEM columns per CTA: never let two CTAs share an SM (the second would spin in tcgen05.alloc)
   constexpr size_t smem_req = smem > 120 * 1024 ? smem : 120 * 1024;
@@ -419,32 +444,32 @@ int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const
     attr_set = true;
   }
   dim3 grid(d.n_qt, d.batch * d.heads);
-  kern<<<grid, kThreads, smem_req, st>>>(tq, tdo, tk, tv, d, abort_flag);
+  kern<<<grid, kThreads, smem_req, st>>>(tq, tdo, tk, tv, tdq, d, abort_flag);
   return cudaGetLastError() == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;
 }
 
 template <int D, int SK>
 int launch_mask(cudaStream_t st, const DevParams& d, int mask, const CUtensorMap& tq, const CUtensorMap& tdo,
-                const CUtensorMap& tk, const CUtensorMap& tv, int* af) {
+                const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdq, int* af) {
   switch (mask) {
-    case FLEXATTN_MASK_NONE: return launch_one<D, SK, FLEXATTN_MASK_NONE>(st, d, tq, tdo, tk, tv, af);
-    case FLEXATTN_MASK_CAUSAL: return launch_one<D, SK, FLEXATTN_MASK_CAUSAL>(st, d, tq, tdo, tk, tv, af);
-    case FLEXATTN_MASK_SLIDING_WINDOW: return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW>(st, d, tq, tdo, tk, tv, af);
+    case FLEXATTN_MASK_NONE: return launch_one<D, SK, FLEXATTN_MASK_NONE>(st, d, tq, tdo, tk, tv, tdq, af);
+    case FLEXATTN_MASK_CAUSAL: return launch_one<D, SK, FLEXATTN_MASK_CAUSAL>(st, d, tq, tdo, tk, tv, tdq, af);
+    case FLEXATTN_MASK_SLIDING_WINDOW: return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW>(st, d, tq, tdo, tk, tv, tdq, af);
     case FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL:
-      return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL>(st, d, tq, tdo, tk, tv, af);
-    case FLEXATTN_MASK_DOCUMENT: return launch_one<D, SK, FLEXATTN_MASK_DOCUMENT>(st, d, tq, tdo, tk, tv, af);
-    case FLEXATTN_MASK_S2: return launch_one<D, SK, FLEXATTN_MASK_S2>(st, d, tq, tdo, tk, tv, af);
+      return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL>(st, d, tq, tdo, tk, tv, tdq, af);
+    case FLEXATTN_MASK_DOCUMENT: return launch_one<D, SK, FLEXATTN_MASK_DOCUMENT>(st, d, tq, tdo, tk, tv, tdq, af);
+    case FLEXATTN_MASK_S2: return launch_one<D, SK, FLEXATTN_MASK_S2>(st, d, tq, tdo, tk, tv, tdq, af);
     default: return FLEXATTN_ERR_UNSUPPORTED_MOD;
   }
 }
 
 template <int D>
 int launch_score(cudaStream_t st, const DevParams& d, int score, int mask, const CUtensorMap& tq,
-                 const CUtensorMap& tdo, const CUtensorMap& tk, const CUtensorMap& tv, int* af) {
+                 const CUtensorMap& tdo, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdq, int* af) {
   switch (score) {
-    case FLEXATTN_SCORE_NONE: return launch_mask<D, FLEXATTN_SCORE_NONE>(st, d, mask, tq, tdo, tk, tv, af);
-    case FLEXATTN_SCORE_ALIBI: return launch_mask<D, FLEXATTN_SCORE_ALIBI>(st, d, mask, tq, tdo, tk, tv, af);
-    case FLEXATTN_SCORE_SOFTCAP: return launch_mask<D, FLEXATTN_SCORE_SOFTCAP>(st, d, mask, tq, tdo, tk, tv, af);
+    case FLEXATTN_SCORE_NONE: return launch_mask<D, FLEXATTN_SCORE_NONE>(st, d, mask, tq, tdo, tk, tv, tdq, af);
+    case FLEXATTN_SCORE_ALIBI: return launch_mask<D, FLEXATTN_SCORE_ALIBI>(st, d, mask, tq, tdo, tk, tv, tdq, af);
+    case FLEXATTN_SCORE_SOFTCAP: return launch_mask<D, FLEXATTN_SCORE_SOFTCAP>(st, d, mask, tq, tdo, tk, tv, tdq, af);
     default: return FLEXATTN_ERR_UNSUPPORTED_MOD;
   }
 }
@@ -454,7 +479,7 @@ int launch_score(cudaStream_t st, const DevParams& d, int score, int mask, const
 int launch_sm100_dq(cudaStream_t st, const DevParams& d, int score, int mask) {
   int* af = abort_flag_ptr();
   if (af == nullptr) return FLEXATTN_ERR_CUDA;
-  CUtensorMap tq, tdo, tk, tv;
+  CUtensorMap tq, tdo, tk, tv, tdq;
   const int slices = d.batch * d.heads;
   int e = make_tile_map(&tq, d.q, slices, d.seq_q, d.head_dim);
   if (e) return e;
@@ -464,8 +489,10 @@ int launch_sm100_dq(cudaStream_t st, const DevParams& d, int score, int mask) {
   if (e) return e;
   e = make_tile_map(&tv, d.v, slices, d.seq_k, d.head_dim);
   if (e) return e;
-  if (d.head_dim == 128) return launch_score<128>(st, d, score, mask, tq, tdo, tk, tv, af);
-  if (d.head_dim == 64) return launch_score<64>(st, d, score, mask, tq, tdo, tk, tv, af);
+  e = make_tile_map(&tdq, d.dq, slices, d.seq_q, d.head_dim);
+  if (e) return e;
+  if (d.head_dim == 128) return launch_score<128>(st, d, score, mask, tq, tdo, tk, tv, tdq, af);
+  if (d.head_dim == 64) return launch_score<64>(st, d, score, mask, tq, tdo, tk, tv, tdq, af);
   return FLEXATTN_ERR_UNSUPPORTED_HEAD_DIM;
 }
 
