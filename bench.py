@@ -177,13 +177,9 @@ class HotPath:
                                             False, self.bf, self.mf, self.sf)
 
     def bwd(self, q, k, v, o, l, m, do):
-        fa = self.fa
-        delta = fa.bwd_preprocess(o, do)
-        dq = fa.flex_attention_bwd_dq(q, k, v, None, self.seg, l, m, o, do, delta, sm_scale=self.sm_scale,
-                                      score_fn=self.sf, mask_fn=self.mf, block_mask_fn=self.bf)
-        dk, dv = fa.flash_attention_bwd_dkv(k, v, q, None, self.seg, l, m, delta, do, sm_scale=self.sm_scale,
-                                            score_fn=self.sf, mask_fn=self.mf, block_mask_fn=self.bf)
-        return dq, dk, dv
+        # delta, then dQ and dK/dV (the package launches the two gradient kernels on two streams)
+        return self.fa.flex_attention_bwd(q, k, v, o, l, m, do, segment_ids=self.seg, sm_scale=self.sm_scale,
+                                          mask_fns=None if self.mf is None else (self.mf, self.bf), score_fn=self.sf)
 
     def step(self, q, k, v, do):
         o, l, m = self.fwd(q, k, v)

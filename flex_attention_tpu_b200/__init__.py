@@ -6,7 +6,7 @@ from . import _binding, masks, scores, util, constants, workloads, sharding  # n
 from .flex_attention_kernel import _flex_attention_impl  # noqa: F401
 from .flex_attention_dq_bwd import flex_attention_bwd_dq, bwd_preprocess  # noqa: F401
 from .flex_attention_dkv_kernel import flash_attention_bwd_dkv  # noqa: F401
-from .flex_attention import flex_attention  # noqa: F401
+from .flex_attention import flex_attention, flex_attention_bwd  # noqa: F401
 
 __all__ = ["_flex_attention_impl", "flex_attention_bwd_dq", "flash_attention_bwd_dkv", "bwd_preprocess",
            "masks", "scores", "util", "constants"]

@@ -255,6 +255,37 @@ class Problem:
         check(lib.flexattn_bwd_dkv(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_dkv")
         return dk, dv
 
+    def backward(self, q, k, v, o, do, l, m, need_dq=True, need_dkv=True):
+        """delta, then dQ and dK/dV.  The two gradient kernels only share inputs, so dK/dV is launched on a side
+        stream: both kernels fill every SM on their own, but the tail of one then overlaps the head of the other.
+        Everything is ordered after the current stream's work and the current stream waits for both."""
+        delta = self.preprocess(o, do)
+        if not (need_dq and need_dkv):
+            dq = self.bwd_dq(q, k, v, do, l, m, delta) if need_dq else None
+            dk, dv = self.bwd_dkv(q, k, v, do, l, m, delta) if need_dkv else (None, None)
+            return delta, dq, dk, dv
+        cur = torch.cuda.current_stream(self.device)
+        side = _side_stream(self.device)
+        dk, dv = self._new(self.shape_k), self._new(self.shape_k)   # allocated on the current stream
+        side.wait_stream(cur)
+        self._bind(q=q, k=k, v=v, d_o=do, l=l, m=m, delta=delta, dk=dk, dv=dv)
+        check(lib.flexattn_bwd_dkv(ctypes.c_void_p(side.cuda_stream), ctypes.byref(self.p)), "flexattn_bwd_dkv")
+        dq = self.bwd_dq(q, k, v, do, l, m, delta)
+        cur.wait_stream(side)
+        return delta, dq, dk, dv
+
+
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device):
+    """One long-lived side stream per device for `Problem.backward` (created on first use)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _SIDE_STREAMS.get(key)
+    if st is None:
+        st = _SIDE_STREAMS[key] = torch.cuda.Stream(device)
+    return st
+
 
 def selftest_umma(variant: int, a: torch.Tensor, b: torch.Tensor, tuning=None, status=None) -> torch.Tensor:
     """Single-tile tensor-core self check (see flexattn_selftest_umma in the header)."""

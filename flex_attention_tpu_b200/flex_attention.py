@@ -27,12 +27,22 @@ class _FlexAttentionFn(torch.autograd.Function):
         q, k, v, o, l, m = ctx.saved_tensors
         prob = ctx.prob
         do = do.contiguous()
-        delta = prob.preprocess(o, do)
-        dq = prob.bwd_dq(q, k, v, do, l, m, delta) if ctx.needs_input_grad[0] else None
-        dk = dv = None
-        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
-            dk, dv = prob.bwd_dkv(q, k, v, do, l, m, delta)
+        _, dq, dk, dv = prob.backward(q, k, v, o, do, l, m, need_dq=ctx.needs_input_grad[0],
+                                      need_dkv=ctx.needs_input_grad[1] or ctx.needs_input_grad[2])
         return dq, dk, dv, None
+
+
+def flex_attention_bwd(q, k, v, o, l, m, do, *, segment_ids=None, causal: bool = False, sm_scale: float = 1.0,
+                       mask_fns=None, score_fn=None, backend: str = "auto"):
+    """The whole backward in one call: delta = rowsum(o * do), then dQ and dK/dV (launched on two streams so
+    that the tail of one kernel overlaps the head of the other).  Residuals ``o, l, m`` as returned by
+    ``_flex_attention_impl(..., save_residuals=True)``; the counterpart of the reference's
+    ``_flash_attention_bwd`` (``jax_exp.py:276-321``).  Returns ``(dq, dk, dv)``."""
+    mask_fn, block_mask_fn = mask_fns if mask_fns is not None else (None, None)
+    prob = make_problem(q, k, ab=None, segment_ids=segment_ids, causal=causal, sm_scale=sm_scale, mask_fn=mask_fn,
+                        block_mask_fn=block_mask_fn, score_fn=score_fn, backend=backend)
+    _, dq, dk, dv = prob.backward(q, k, v, o, do.contiguous(), l, m)
+    return dq, dk, dv
 
 
 def flex_attention(q, k, v, ab=None, segment_ids=None, *, causal: bool = False, sm_scale: float = 1.0,

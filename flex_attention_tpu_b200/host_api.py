@@ -13,8 +13,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from .flex_attention_dkv_kernel import flash_attention_bwd_dkv
-from .flex_attention_dq_bwd import bwd_preprocess, flex_attention_bwd_dq
+from .flex_attention import flex_attention_bwd
 from .flex_attention_kernel import _flex_attention_impl
 
 
@@ -71,12 +70,10 @@ def fwd_bwd_from_host(q, k, v, do, *, sm_scale, mask_fn=None, block_mask_fn=None
             seg = None if seg_dev is None else seg_dev[b0:b1].contiguous()
             o, l, m = _flex_attention_impl(qd, kd, vd, None, seg, True, causal, sm_scale, 1, 128, 128, 128, False,
                                            block_mask_fn, mask_fn, score_fn, backend=backend)
-            delta = bwd_preprocess(o, dod)
-            dq = flex_attention_bwd_dq(qd, kd, vd, None, seg, l, m, o, dod, delta, sm_scale=sm_scale, score_fn=score_fn,
-                                       mask_fn=mask_fn, block_mask_fn=block_mask_fn, causal=causal, backend=backend)
-            dk, dv = flash_attention_bwd_dkv(kd, vd, qd, None, seg, l, m, delta, dod, sm_scale=sm_scale, causal=causal,
-                                             score_fn=score_fn, mask_fn=mask_fn, block_mask_fn=block_mask_fn,
-                                             backend=backend)
+            dq, dk, dv = flex_attention_bwd(qd, kd, vd, o, l, m, dod, segment_ids=seg, causal=causal, sm_scale=sm_scale,
+                                            mask_fns=None if mask_fn is None else (mask_fn, block_mask_fn),
+                                            score_fn=score_fn, backend=backend)
+            delta = None
             ev_comp = torch.cuda.Event()
             ev_comp.record(s_comp)
             ev_comp_done[slot] = ev_comp
