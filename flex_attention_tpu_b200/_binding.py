@@ -260,7 +260,7 @@ class Problem:
         stream: both kernels fill every SM on their own, but the tail of one then overlaps the head of the other.
         Everything is ordered after the current stream's work and the current stream waits for both."""
         delta = self.preprocess(o, do)
-        if not (need_dq and need_dkv):
+        if not (need_dq and need_dkv and TWO_STREAM_BACKWARD):
             dq = self.bwd_dq(q, k, v, do, l, m, delta) if need_dq else None
             dk, dv = self.bwd_dkv(q, k, v, do, l, m, delta) if need_dkv else (None, None)
             return delta, dq, dk, dv
@@ -276,6 +276,8 @@ class Problem:
 
 
 _SIDE_STREAMS = {}
+# dK/dV on a side stream next to dQ (see Problem.backward); False launches the two kernels one after the other
+TWO_STREAM_BACKWARD = True
 
 
 def _side_stream(device):
