@@ -24,16 +24,24 @@
 #include "sm100.cuh"
 
 #ifdef FLEXATTN_TRACE
+#ifdef FLEXATTN_TRACE_WARPS
+#define FA_TRACE(slot)
+#else
 #define FA_TRACE(slot)                                                          \
   do {                                                                          \
     if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64)     \
       P.trace[n * 16 + (slot)] = clock64();                                     \
   } while (0)
+#endif
+#ifdef FLEXATTN_TRACE_WARPS
+#define FA_TRACE_AT(idx, slot)
+#else
 #define FA_TRACE_AT(idx, slot)                                                           \
   do {                                                                                   \
     if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (idx) >= 0 && (idx) < 64) \
       P.trace[(idx) * 16 + (slot)] = clock64();                                          \
   } while (0)
+#endif
 #else
 #define FA_TRACE(slot)
 #define FA_TRACE_AT(idx, slot)
@@ -361,35 +369,52 @@ __global__ void __launch_bounds__(kThreads, 1)
     // Statistics of the query rows (l, m, delta, document id) are fetched from global memory one tile ahead
     // into registers, so their latency is off the critical path.
     const size_t stat_base = (size_t)bh * P.seq_q;
-    float pf_l = 0.f, pf_m = 0.f, pf_d = 0.f;
-    int pf_doc = -1;
+    // Division of the staging work inside a warpgroup (all of it one tile ahead): threads 0..63 own one query row
+    // each for -(m log2e + log2 l) - l and m fetched into registers a tile earlier, one shared-memory store;
+    // threads 64..127 own one row each for delta (and the document id), which needs no arithmetic and goes
+    // global -> shared with cp.async, costing the thread nothing.  Shared-memory stores are slow while the MMAs
+    // saturate shared memory, so no warp issues more than one per tile.
+    float pf_l = 0.f, pf_m = 0.f;
     bool pf_ok = false;
-    auto fetch_stats = [&](int n) {
+    auto fetch_stats = [&](int n) {  // threads 0..63
       const int i = (cm.x + n) * kTile + 64 * half + row;
       pf_ok = i < P.seq_q;
       if (pf_ok) {
         pf_l = P.l[stat_base + i];
         pf_m = P.m[stat_base + i];
-        pf_d = P.delta[stat_base + i];
-        if (MK == FLEXATTN_MASK_DOCUMENT) pf_doc = doc[i];
       }
     };
-    if (row < 64 && N > 0) fetch_stats(0);
+    auto stage_stats = [&](int n) {
+      const int st = n & 1;
+      if (row < 64) {
+        // pre-scaled for pack_bf16_trunc; l == 0 (fully masked row) forces p to 0
+        sh->nlse2[st][64 * half + row] =
+            pf_ok ? (pf_l > 0.f ? ptx::kRoundLog2 - fmaf(pf_m, kLog2e, log2f(pf_l)) : -1.0e30f) : ptx::kRoundLog2;
+      } else {
+        const int r = row - 64;
+        const int i = (cm.x + n) * kTile + 64 * half + r;
+        if (i < P.seq_q) {
+          ptx::cp_async4(&sh->delta[st][64 * half + r], &P.delta[stat_base + i]);
+          if (MK == FLEXATTN_MASK_DOCUMENT) ptx::cp_async4(&sh->doc[st][64 * half + r], &doc[i]);
+        } else {
+          sh->delta[st][64 * half + r] = 0.f;
+          if (MK == FLEXATTN_MASK_DOCUMENT) sh->doc[st][64 * half + r] = -1;
+        }
+      }
+    };
+    if (N > 0) {
+      if (row < 64) fetch_stats(0);
+      stage_stats(0);
+      if (row < 64 && N > 1) fetch_stats(1);
+    }
 
     for (int n = 0; n < N; ++n) {
       const int st = n & 1;
       const int qt = cm.x + n, i0 = qt * kTile + 64 * half;  // first query position of this warpgroup's columns
       const bool partial = !(qt >= cm.z && qt < cm.w);
-      if (row < 64) {
-        // threads 0..63 of the warpgroup stage one query row each
-        // l == 0 (fully masked row): force p to 0; kRoundLog2 pre-scales p for pack_bf16_trunc
-        sh->nlse2[st][64 * half + row] =
-            pf_ok ? (pf_l > 0.f ? ptx::kRoundLog2 - fmaf(pf_m, kLog2e, log2f(pf_l)) : -1.0e30f) : ptx::kRoundLog2;
-        sh->delta[st][64 * half + row] = pf_ok ? pf_d : 0.f;
-        if (MK == FLEXATTN_MASK_DOCUMENT) sh->doc[st][64 * half + row] = pf_ok ? pf_doc : -1;
-        if (n + 1 < N) fetch_stats(n + 1);
-      }
+      // the statistics of this tile were staged during the previous tile (or before the loop)
       // a failed wait never leaves the loop early: every thread keeps executing the same named barriers
+      ptx::cp_async_wait_all();  // this thread's asynchronous copies for this tile have landed
       ptx::named_bar_sync(1 + half, 128);
       if (tid == 0) FA_TRACE(8);
       if (!ok) continue;
@@ -427,7 +452,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(&sh->bar_p);
       }
+#ifdef FLEXATTN_TRACE_WARPS
+      if (lane == 0 && P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64) P.trace[n * 16 + warp] = clock64();
+#else
       if (tid == 0) FA_TRACE(10);
+#endif
+      // While dP^T of this tile is still being computed: stage the statistics of the NEXT tile (its stage was last
+      // read two tiles ago) and fetch those of the one after.  Done here, the shared-memory stores - slow while
+      // the MMAs saturate shared memory - overlap a wait instead of delaying the first phase.
+      if (n + 1 < N) {
+        stage_stats(n + 1);
+        if (row < 64 && n + 2 < N) fetch_stats(n + 2);
+      }
       load_stats32(st0, &sh->delta[st][64 * half]);
       ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dp, n & 1));
       if (!ok) { fail_at = 11; continue; }
@@ -450,6 +486,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(&sh->bar_ds);
       }
+#ifdef FLEXATTN_TRACE_WARPS
+      if (lane == 0 && P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64) P.trace[n * 16 + 8 + warp] = clock64();
+#endif
       if (tid == 0) FA_TRACE(12);
     }
 

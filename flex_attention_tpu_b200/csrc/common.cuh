@@ -30,7 +30,7 @@ constexpr int32_t kMapMagic = 0x464c5841;  // "FLXA"
 
 struct MapLayout {
   int n_qt, n_kt, rows, n_t;
-  size_t off_row, off_col, off_doc, bytes;
+  size_t off_row, off_col, off_doc, off_order, bytes;
 };
 
 __host__ __device__ inline MapLayout map_layout(int batch, int seq_q, int seq_k, int mask_kind) {
@@ -43,7 +43,10 @@ __host__ __device__ inline MapLayout map_layout(int batch, int seq_q, int seq_k,
   L.off_col = L.off_row + sizeof(int4) * (size_t)L.rows * L.n_qt;
   L.off_doc = L.off_col + sizeof(int4) * (size_t)L.rows * L.n_kt;
   size_t doc = (mask_kind == FLEXATTN_MASK_DOCUMENT) ? sizeof(int2) * (size_t)batch * L.n_t : 0;
-  L.bytes = (L.off_doc + doc + 255) & ~(size_t)255;
+  // q tiles of every map row ordered by their number of kv tiles, largest first (work order of the persistent
+  // forward kernel)
+  L.off_order = (L.off_doc + doc + 15) & ~(size_t)15;
+  L.bytes = (L.off_order + sizeof(int32_t) * (size_t)L.rows * L.n_qt + 255) & ~(size_t)255;
   return L;
 }
 
@@ -64,6 +67,7 @@ struct DevParams {
   const float* alibi_slopes;
   const int4* row_map;  // [rows][n_qt]
   const int4* col_map;  // [rows][n_kt]
+  const int32_t* order;  // [rows][n_qt]: q tiles by decreasing number of kv tiles
   int32_t* status;
   long long* trace;  // per-phase cycle stamps of one CTA; only written by builds with FLEXATTN_TRACE
   int batch, heads, seq_q, seq_k, head_dim;
