@@ -24,6 +24,17 @@
 // 2 V tiles (192 KB for D = 128).
 #include "sm100.cuh"
 
+#ifdef FLEXATTN_TRACE
+// cycle stamps of CTA 0, one row of 16 slots per kv tile of its stream (first 64 tiles)
+#define FA_TRACE_T(T, slot)                                                     \
+  do {                                                                          \
+    if (P.trace != nullptr && blockIdx.x == 0 && (T) < 64)                      \
+      P.trace[(T) * 16 + (slot)] = clock64();                                   \
+  } while (0)
+#else
+#define FA_TRACE_T(T, slot)
+#endif
+
 
 namespace flexattn {
 namespace {
@@ -323,8 +334,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (pn == 0) pN = sh->item_tiles[pqi & 7];  // written before the Q K^T position passed this item
         ok = ptx::mbar_wait(&sh->bar_p[psb], psph);
         if (!ok) { fail_at = 4; break; }
+        FA_TRACE_T(pT, 0);
         ok = ptx::mbar_wait(&sh->bar_v[pT & 1], (pT >> 1) & 1);
         if (!ok) { fail_at = 5; break; }
+        FA_TRACE_T(pT, 1);
         ptx::tc_fence_after();
         const ptx::DescBase bv = (pT & 1) ? bV1 : bV0;
 #pragma unroll
@@ -332,6 +345,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::mma_ts(tmem + kColO, tmem + psb * 128u + kk * 8, ptx::desc_at(bv, ptx::koff_mnmajor(kk)), idesc_pv,
                       (pn > 0) || (kk > 0));
         ptx::mma_commit(&sh->bar_pv[psb]);
+        FA_TRACE_T(pT, 2);
         ++pT;
         if (++psb == kSBufs) { psb = 0; psph ^= 1u; }
         if (++pn == pN) {
@@ -339,6 +353,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           ++pqi;
         }
         if (!q_end) issue_qk();
+        FA_TRACE_T(pT - 1, 3);
       }
       if (!ok) give_up(abort_flag, P.status, 4, fail_at);
     }
@@ -382,6 +397,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_s[sb], sph));
           if (!ok) fail_at = 10;
         }
+        if (tid == 0) FA_TRACE_T(T, 8);
         float x[kHalf];
         if (ok) {
           ptx::tc_fence_after();
@@ -422,8 +438,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             xs = c2;
           }
         }
+        if (tid == 0) FA_TRACE_T(T, 9);
         sh->pmax[par][half][row] = tmax;
         ptx::named_bar_sync(1, 256);  // exchange the partial row maxima of the two halves
+        if (tid == 0) FA_TRACE_T(T, 10);
         if (ok) {
           tmax = fmaxf(tmax, sh->pmax[par][half ^ 1][row]);
           m_true = fmaxf(m_true, tmax);
@@ -465,6 +483,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             ls2[(c >> 1) & 1] = ptx::add2(ls2[(c >> 1) & 1], ptx::pack2(p0, p1));
             pk[c >> 1] = ptx::pack_bf16_trunc(p0, p1);
           }
+          if (tid == 0) FA_TRACE_T(T, 11);
           ptx::tmem_st32(lane_base + colS + (c_base >> 1), pk);
           {
             float s0, s1;
@@ -474,6 +493,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           ptx::mbar_arrive(&sh->bar_p[sb]);
+          if (tid == 0) FA_TRACE_T(T, 12);
         }
         if (++sb == kSBufs) { sb = 0; sph ^= 1u; }
       }
