@@ -48,7 +48,9 @@ def _install_shims():
 
 
 def main():
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of the reference project>")
+    ref_dir = sys.argv[1]
     _install_shims()
     sys.path.insert(0, ref_dir)
     import mha_reference as ref      # noqa: E402  (reference mha_reference.py)
