@@ -20,6 +20,7 @@ SCORE_NONE, SCORE_ALIBI, SCORE_SOFTCAP = 0, 1, 2
 MASK_NONE, MASK_CAUSAL, MASK_SLIDING_WINDOW, MASK_SLIDING_WINDOW_CAUSAL, MASK_DOCUMENT, MASK_S2 = range(6)
 BACKEND_AUTO, BACKEND_SIMT, BACKEND_TCGEN05 = 0, 1, 2
 TILE = 128
+ABI_VERSION = 2   # FLEXATTN_ABI_VERSION of include/flexattn.h this binding was written against
 
 MASK_KIND_IDS = {"none": MASK_NONE, "causal": MASK_CAUSAL, "sliding_window": MASK_SLIDING_WINDOW,
                  "sliding_window_causal": MASK_SLIDING_WINDOW_CAUSAL, "document": MASK_DOCUMENT, "s2": MASK_S2}
@@ -40,6 +41,7 @@ class FlexAttnParams(ctypes.Structure):
         ("mask_kind", ctypes.c_int32), ("window", ctypes.c_int32), ("stride", ctypes.c_int32),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("status", ctypes.c_void_p), ("backend", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("ab", ctypes.c_void_p), ("dab", ctypes.c_void_p),
     ]
 
 
@@ -76,7 +78,7 @@ def _load():
     lib.flexattn_selftest_umma.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
                                            ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p,
                                            ctypes.POINTER(ctypes.c_int32)]
-    if lib.flexattn_abi_version() != 1:
+    if lib.flexattn_abi_version() != ABI_VERSION:
         raise ImportError("libflexattn.so ABI version mismatch: rebuild the library")
     return lib
 
@@ -109,7 +111,7 @@ class Problem:
     _MAP_CACHE_ENTRIES = 16
 
     def __init__(self, q, k, *, sm_scale, mask_kind=MASK_NONE, window=0, stride=0, doc_ids=None,
-                 score_kind=SCORE_NONE, softcap=0.0, alibi_slopes=None, backend=BACKEND_AUTO, status=None):
+                 score_kind=SCORE_NONE, softcap=0.0, alibi_slopes=None, backend=BACKEND_AUTO, status=None, ab=None):
         if not q.is_cuda:
             raise ValueError("flex attention tensors must live on a CUDA device (no CPU path exists)")
         if q.dim() != 4 or k.dim() != 4:
@@ -148,6 +150,16 @@ class Problem:
         if status is not None:
             p.status = status.data_ptr()
             self._keep.append(status)
+        self.ab = None
+        if ab is not None:
+            # dense additive bias [B,H,Sq,Sk], float32 (SIMT backend; the library refuses it on tcgen05)
+            if not (isinstance(ab, torch.Tensor) and ab.is_cuda):
+                raise ValueError("ab must be a CUDA tensor")
+            if tuple(ab.shape) != (B, H, Sq, k.shape[2]):
+                raise ValueError(f"Attention bias shape mismatch: expected {(B, H, Sq, k.shape[2])}, got {tuple(ab.shape)}")
+            self.ab = ab.to(torch.float32).contiguous()
+            p.ab = self.ab.data_ptr()
+            self._keep.append(self.ab)
         self.p = p
         self._bind_workspace()
 
@@ -243,11 +255,21 @@ class Problem:
         check(lib.flexattn_bwd_preprocess(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_preprocess")
         return delta
 
-    def bwd_dq(self, q, k, v, do, l, m, delta):
+    def bwd_dq(self, q, k, v, do, l, m, delta, want_dab=False):
+        """dq, or (dq, dab) with ``want_dab`` (dab: float32 [B,H,Sq,Sk], the gradient of the dense bias)."""
         dq = self._new(self.shape_q)
         self._bind(q=q, k=k, v=v, d_o=do, l=l, m=m, delta=delta, dq=dq)
-        check(lib.flexattn_bwd_dq(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_dq")
-        return dq
+        dab = None
+        if want_dab:
+            if self.ab is None:
+                raise ValueError("dab was requested but the problem has no bias `ab`")
+            dab = torch.empty_like(self.ab)
+            self.p.dab = dab.data_ptr()
+        try:
+            check(lib.flexattn_bwd_dq(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_dq")
+        finally:
+            self.p.dab = None
+        return (dq, dab) if want_dab else dq
 
     def bwd_dkv(self, q, k, v, do, l, m, delta):
         dk, dv = self._new(self.shape_k), self._new(self.shape_k)
@@ -255,11 +277,15 @@ class Problem:
         check(lib.flexattn_bwd_dkv(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_dkv")
         return dk, dv
 
-    def backward(self, q, k, v, o, do, l, m, need_dq=True, need_dkv=True):
+    def backward(self, q, k, v, o, do, l, m, need_dq=True, need_dkv=True, want_dab=False):
         """delta, then dQ and dK/dV.  The two gradient kernels only share inputs, so dK/dV is launched on a side
         stream: both kernels fill every SM on their own, but the tail of one then overlaps the head of the other.
         Everything is ordered after the current stream's work and the current stream waits for both."""
         delta = self.preprocess(o, do)
+        if want_dab:  # the bias gradient comes out of the dQ kernel
+            dq, dab = self.bwd_dq(q, k, v, do, l, m, delta, want_dab=True)
+            dk, dv = self.bwd_dkv(q, k, v, do, l, m, delta) if need_dkv else (None, None)
+            return delta, dq, dk, dv, dab
         if not (need_dq and need_dkv and TWO_STREAM_BACKWARD):
             dq = self.bwd_dq(q, k, v, do, l, m, delta) if need_dq else None
             dk, dv = self.bwd_dkv(q, k, v, do, l, m, delta) if need_dkv else (None, None)

@@ -10,9 +10,6 @@ from . import masks, scores
 
 def make_problem(q, k, *, ab, segment_ids, causal, sm_scale, mask_fn, block_mask_fn, score_fn, backend="auto",
                  status=None) -> B.Problem:
-    if ab is not None:
-        raise NotImplementedError("dense additive bias `ab` is not supported by the CUDA kernels; "
-                                  "use a score_fn from flex_attention_tpu_b200.scores (e.g. ALiBi)")
     if not isinstance(q, torch.Tensor):
         raise TypeError("flex attention expects torch CUDA tensors")
     mspec = masks.spec_of(mask_fn, block_mask_fn)
@@ -40,7 +37,7 @@ def make_problem(q, k, *, ab, segment_ids, causal, sm_scale, mask_fn, block_mask
             raise ValueError("document mask needs doc_lengths or segment_ids")
     kw = dict(sm_scale=sm_scale, mask_kind=B.MASK_KIND_IDS[mspec.kind], window=mspec.window, stride=mspec.stride,
               doc_ids=doc_ids, backend=B.BACKEND_IDS[backend] if isinstance(backend, str) else backend,
-              status=status)
+              status=status, ab=ab)
     if sspec is not None:
         kw.update(score_kind=B.SCORE_KIND_IDS[sspec.kind], softcap=sspec.cap, alibi_slopes=sspec.slopes)
     return B.Problem(q, k, **kw)

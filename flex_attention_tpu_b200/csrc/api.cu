@@ -46,7 +46,8 @@ int validate_workspace(const FlexAttnParams* p) {
 
 // true when the tensor-core kernels serve this problem
 bool use_tcgen05(const FlexAttnParams* p, int* err) {
-  const bool capable = p->dtype == FLEXATTN_BF16 && (p->head_dim == 64 || p->head_dim == 128);
+  // the tensor-core kernels take bf16, D in {64, 128} and no dense bias
+  const bool capable = p->dtype == FLEXATTN_BF16 && (p->head_dim == 64 || p->head_dim == 128) && p->ab == nullptr;
   *err = FLEXATTN_OK;
   if (p->backend == FLEXATTN_BACKEND_SIMT) return false;
   if (p->backend == FLEXATTN_BACKEND_TCGEN05 && !capable) *err = FLEXATTN_ERR_UNSUPPORTED_BACKEND;
@@ -69,6 +70,8 @@ DevParams make_dev(const FlexAttnParams* p) {
   d.l = p->l; d.m = p->m; d.delta = p->delta;
   d.doc_ids = p->mask_kind == FLEXATTN_MASK_DOCUMENT ? p->doc_ids : nullptr;
   d.alibi_slopes = p->score_kind == FLEXATTN_SCORE_ALIBI ? p->alibi_slopes : nullptr;
+  d.ab = p->ab;
+  d.dab = p->dab;
   d.row_map = reinterpret_cast<const int4*>(ws + L.off_row);
   d.col_map = reinterpret_cast<const int4*>(ws + L.off_col);
   d.order = reinterpret_cast<const int32_t*>(ws + L.off_order);

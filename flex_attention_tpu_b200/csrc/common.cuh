@@ -65,6 +65,8 @@ struct DevParams {
   float* delta;
   const int32_t* doc_ids;
   const float* alibi_slopes;
+  const float* ab;  // optional dense bias [B,H,Sq,Sk] (SIMT backend only)
+  float* dab;       // optional bias gradient, written by the SIMT dQ kernel
   const int4* row_map;  // [rows][n_qt]
   const int4* col_map;  // [rows][n_kt]
   const int32_t* order;  // [rows][n_qt]: q tiles by decreasing number of kv tiles

@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(kWarps * 32) simt_fwd_kernel(DevParams P, int 
     if (valid) {
       float s = dot_row<D>(k + (size_t)j * D, s_q[warp]) * P.sm_scale;
       if (keep_rt(mask, i, j, P.window, P.stride, di, doc ? doc[j] : 0))
-        x = score_rt(score, s, i, j, slope, P.cap, inv_cap);
+        x = score_rt(score, s, i, j, slope, P.cap, inv_cap) + (P.ab ? P.ab[(size_t)row * P.seq_k + j] : 0.f);
     }
     float mx = x;
 #pragma unroll
@@ -156,16 +156,23 @@ __global__ void __launch_bounds__(kWarps * 32) simt_dq_kernel(DevParams P, int s
   float acc[D / 32];
 #pragma unroll
   for (int t = 0; t < D / 32; ++t) acc[t] = 0.f;
+  if (P.dab) {  // the bias gradient is dense: zero outside the kv tiles this row visits
+    float* dab_row = P.dab + (size_t)row * P.seq_k;
+    for (int j = lane; j < kbeg; j += 32) dab_row[j] = 0.f;
+    for (int j = kend + lane; j < P.seq_k; j += 32) dab_row[j] = 0.f;
+  }
   for (int j0 = kbeg; j0 < kend; j0 += 32) {
     const int j = j0 + lane;
-    float ds = 0.f;
+    float ds = 0.f, dt = 0.f;  // dt: gradient of the logit after the score function (what the bias sees)
     if (j < kend && keep_rt(mask, i, j, P.window, P.stride, di, doc ? doc[j] : 0)) {
       const float s = dot_row<D>(k + (size_t)j * D, s_q[warp]) * P.sm_scale;
-      const float x = score_rt(score, s, i, j, slope, P.cap, inv_cap);
+      const float x = score_rt(score, s, i, j, slope, P.cap, inv_cap) + (P.ab ? P.ab[(size_t)row * P.seq_k + j] : 0.f);
       const float p = __expf(x - m) * inv_l;
       const float dp = dot_row<D>(v + (size_t)j * D, s_do[warp]);
-      ds = p * (dp - delta) * dsig_rt(score, s, inv_cap) * P.sm_scale;
+      dt = p * (dp - delta);
+      ds = dt * dsig_rt(score, s, inv_cap) * P.sm_scale;
     }
+    if (P.dab && j < kend) P.dab[(size_t)row * P.seq_k + j] = dt;
     const int n = min(32, kend - j0);
     for (int jj = 0; jj < n; ++jj) {
       const float dsj = __shfl_sync(0xffffffffu, ds, jj);
@@ -212,7 +219,8 @@ __global__ void __launch_bounds__(kWarps * 32) simt_dkv_kernel(DevParams P, int 
     float p = 0.f, ds = 0.f;
     if (i < qend && keep_rt(mask, i, j, P.window, P.stride, doc ? doc[i] : 0, dj)) {
       const float s = dot_row<D>(q + (size_t)i * D, s_k[warp]) * P.sm_scale;
-      const float x = score_rt(score, s, i, j, slope, P.cap, inv_cap);
+      const float x = score_rt(score, s, i, j, slope, P.cap, inv_cap) +
+                      (P.ab ? P.ab[((size_t)bh * P.seq_q + i) * P.seq_k + j] : 0.f);
       const float l = lrow[i];
       p = __expf(x - mrow[i]) * (l > 0.f ? 1.f / l : 0.f);
       const float dp = dot_row<D>(dO + (size_t)i * D, s_v[warp]);

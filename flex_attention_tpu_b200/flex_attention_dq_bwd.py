@@ -15,8 +15,13 @@ def bwd_preprocess(o, do):
 
 def flex_attention_bwd_dq(q, k, v, ab, segment_ids, l, m, o, do, d, *, block_b=None, block_q=None,
                           block_k_major=None, block_k=None, sm_scale=1.0, debug=False, score_fn=None,
-                          mask_fn=None, block_mask_fn=None, causal=False, backend="auto", status=None):
+                          mask_fn=None, block_mask_fn=None, causal=False, backend="auto", status=None,
+                          return_dab=False):
     """dq = sm_scale * (p * (do v^T - d) * score_mod'(s)) k, with p rebuilt from (l, m).
+
+    ``ab``: optional dense additive bias [B, H, Sq, Sk] (float32; served by the SIMT backend).  With
+    ``return_dab`` the call returns ``(dq, dab)``, dab = p * (do v^T - d), the gradient of ``ab``
+    ("dab is just ds", reference ``jax_exp.py:1676-1677``).
 
     ``d`` is delta = rowsum(o * do) ([B, H, Sq] float32); pass ``None`` to have it computed here from
     ``o`` and ``do``.  ``o`` is otherwise unused, as in the reference kernel.  ``block_*`` / ``debug`` are
@@ -26,4 +31,4 @@ def flex_attention_bwd_dq(q, k, v, ab, segment_ids, l, m, o, do, d, *, block_b=N
                         block_mask_fn=block_mask_fn, score_fn=score_fn, backend=backend, status=status)
     if d is None:
         d = prob.preprocess(o, do)
-    return prob.bwd_dq(q, k, v, do, l, m, d)
+    return prob.bwd_dq(q, k, v, do, l, m, d, want_dab=return_dab)

@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define FLEXATTN_ABI_VERSION 1
+#define FLEXATTN_ABI_VERSION 2
 #define FLEXATTN_TILE 128 /* q-tile and kv-tile edge used by the mask map and by every kernel */
 
 typedef enum FlexAttnStatus {
@@ -109,6 +109,14 @@ typedef struct FlexAttnParams {
   int32_t* status;
   int32_t backend;            /* FlexAttnBackend */
   int32_t reserved;
+  /* optional dense additive bias, float32 [B,H,Sq,Sk], added to the logits after the score function and before
+   * the mask (the reference's `ab`: flex_attention_kernel.py:262-266, mha_reference.py:50-51).  NULL = none.
+   * Served by the SIMT backend only: with a bias, FLEXATTN_BACKEND_AUTO selects it and
+   * FLEXATTN_BACKEND_TCGEN05 fails with FLEXATTN_ERR_UNSUPPORTED_BACKEND. */
+  const float* ab;
+  /* optional gradient of the bias, float32 [B,H,Sq,Sk], written by flexattn_bwd_dq when not NULL:
+   * dab = p * (dp - delta), zero at masked pairs ("dab is just ds", jax_exp.py:1676-1677). */
+  float* dab;
 } FlexAttnParams;
 
 /* ABI version of the loaded library (== FLEXATTN_ABI_VERSION of the header it was built from). */

@@ -155,8 +155,9 @@ def delta_reference(o, do):
 
 def mha_bwd_reference(q, k, v, o, do, l, m, ab=None, *, sm_scale=1.0,
                       mask_kind="none", window=None, stride=None, doc_ids=None,
-                      score_kind="none", cap=None, alibi_slopes=None, block_rows=1024):
-    """Dense backward mirroring ``mha_reference.py:112-237``.  Returns (dq, dk, dv) in f32."""
+                      score_kind="none", cap=None, alibi_slopes=None, block_rows=1024, return_dab=False):
+    """Dense backward mirroring ``mha_reference.py:112-237``.  Returns (dq, dk, dv) in f32, plus the gradient of
+    the dense bias ``ab`` ([B,H,Sq,Sk]) with ``return_dab``."""
     q = np.asarray(q, dtype=np.float32)
     k = np.asarray(k, dtype=np.float32)
     v = np.asarray(v, dtype=np.float32)
@@ -169,6 +170,7 @@ def mha_bwd_reference(q, k, v, o, do, l, m, ab=None, *, sm_scale=1.0,
     dq = np.zeros((B, H, Sq, D), np.float32)
     dk = np.zeros((B, H, Sk, D), np.float32)
     dv = np.zeros((B, H, Sk, D), np.float32)
+    dab = np.zeros((B, H, Sq, Sk), np.float32) if return_dab else None
     c = np.float32(sm_scale)
     for b in range(B):
         for h in range(H):
@@ -189,12 +191,14 @@ def mha_bwd_reference(q, k, v, o, do, l, m, ab=None, *, sm_scale=1.0,
                 dp = dob @ v[b, h, :kl].T                              # :216
                 sum_d = (dob * o[b, h, q0:q1]).sum(axis=-1, dtype=np.float32)  # :220
                 ds = p * (dp - sum_d[:, None])                         # :221
+                if dab is not None:
+                    dab[b, h, q0:q1, :kl] = ds                         # "dab is just ds", jax_exp.py:1676-1677
                 if dsig is not None:
                     ds = ds * dsig
                 ds = ds * c                                            # :229
                 dq[b, h, q0:q1] = ds @ k[b, h, :kl]                    # :230
                 dk[b, h, :kl] += ds.T @ q[b, h, q0:q1]                 # :231
-    return dq, dk, dv
+    return (dq, dk, dv, dab) if return_dab else (dq, dk, dv)
 
 
 # ----------------------------------------------------------------------------------------------

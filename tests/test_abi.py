@@ -30,7 +30,7 @@ def test_every_declared_symbol_is_exported(B):
 
 def test_struct_layout_matches_header(B):
     # 13 pointers, 5+1 ints, float, int, float, 3 ints, pointer, size_t, pointer, 2 ints
-    assert ctypes.sizeof(B.FlexAttnParams) == 184
+    assert ctypes.sizeof(B.FlexAttnParams) == 200
     assert B.FlexAttnParams.workspace.offset == 152 and B.FlexAttnParams.status.offset == 168
 
 
@@ -38,7 +38,7 @@ def test_status_strings(B):
     assert B.status_string(0) == "ok"
     assert "workspace" in B.status_string(6)
     assert B.status_string(12345) == "unknown status"
-    assert B.lib.flexattn_abi_version() == 1
+    assert B.lib.flexattn_abi_version() == 2
 
 
 def test_workspace_bytes(B):
@@ -95,6 +95,6 @@ def test_python_layer_rejects_what_the_kernels_cannot_run():
     q = torch.zeros(1, 1, 128, 64)
     with pytest.raises(ValueError):                                       # CPU tensors: no CPU path exists
         fa._flex_attention_impl(q, q, q, None, None, True, True, 1.0, 1, 128, 128, 128, False, None, None, None)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError):                                       # the dense bias must be a CUDA tensor too
         fa._flex_attention_impl(q, q, q, np.zeros(1), None, True, True, 1.0, 1, 128, 128, 128, False, None, None,
                                 None)

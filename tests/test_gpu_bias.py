@@ -1,0 +1,61 @@
+"""Dense additive bias `ab` [B,H,Sq,Sk] (reference: flex_attention_kernel.py:262-266, mha_reference.py:50-51)
+and its gradient `dab` ("dab is just ds", jax_exp.py:1676-1677), served by the SIMT backend."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL, assert_close, build_mods, errors, make_qkvdo
+from oracle import mha_reference_cpu as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(fa, q, k, v, do, ab, *, sm_scale, mask_kind, score_kind, doc, cap):
+    mf, bf, sf, seg = build_mods(fa, mask_kind, score_kind, doc_ids=doc, cap=cap)
+    o, l, m = fa._flex_attention_impl(q, k, v, ab, seg, True, False, sm_scale, 1, 128, 128, 128, False, bf, mf, sf)
+    delta = fa.bwd_preprocess(o, do)
+    dq, dab = fa.flex_attention_bwd_dq(q, k, v, ab, seg, l, m, o, do, delta, sm_scale=sm_scale, score_fn=sf,
+                                       mask_fn=mf, block_mask_fn=bf, return_dab=True)
+    dk, dv = fa.flash_attention_bwd_dkv(k, v, q, ab, seg, l, m, delta, do, sm_scale=sm_scale, score_fn=sf,
+                                        mask_fn=mf, block_mask_fn=bf)
+    torch.cuda.synchronize()
+    return dict(o=o, l=l, m=m, dq=dq, dk=dk, dv=dv, dab=dab)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mask_kind,score_kind", [("none", "none"), ("causal", "none"), ("document", "softcap")])
+def test_bias_forward_and_backward(mask_kind, score_kind, dtype):
+    import flex_attention_tpu_b200 as fa
+    B, H, Sq, Sk, D = 2, 3, 200, 333 if mask_kind == "none" else 200, 64
+    (q, k, v, do), host = make_qkvdo((B, H, Sq, D), (B, H, Sk, D), 31, dtype)
+    rng = np.random.default_rng(7)
+    ab_h = (0.7 * rng.standard_normal((B, H, Sq, Sk))).astype(np.float32)
+    ab = torch.from_numpy(ab_h).cuda()
+    doc = fa.workloads.draw_documents(np.random.default_rng(3), B, Sq, lo=30, hi=120)[0] if mask_kind == "document" else None
+    cap = 5.0 if score_kind == "softcap" else 0.0
+    got = _run(fa, q, k, v, do, ab, sm_scale=0.12, mask_kind=mask_kind, score_kind=score_kind, doc=doc, cap=cap)
+    kw = dict(sm_scale=0.12, mask_kind=mask_kind, doc_ids=doc, score_kind=score_kind, cap=cap or None)
+    qh, kh, vh, doh = host
+    o, l, m = oracle.mha_reference(qh, kh, vh, ab_h, save_residuals=True, **kw)
+    dq, dk, dv, dab = oracle.mha_bwd_reference(qh, kh, vh, o, doh, l, m, ab_h, return_dab=True, **kw)
+    want = dict(o=o, l=l, m=m, dq=dq, dk=dk, dv=dv)
+    assert_close(got, want, dtype, what=f"bias {mask_kind}/{score_kind}")
+    # dab is float32 in both cases; with bf16 inputs delta comes from the bf16-rounded o, hence the relative bound
+    e = errors(got["dab"], dab)
+    assert (e["max_abs"] <= 2e-3) if dtype == torch.float32 else (e["max_rel"] <= TOL[torch.bfloat16]["rel"]), e
+
+
+def test_bias_gets_a_gradient_through_autograd_and_is_refused_by_tcgen05():
+    import flex_attention_tpu_b200 as fa
+    from flex_attention_tpu_b200._binding import FlexAttnError
+    (q, k, v, do), _ = make_qkvdo((1, 2, 256, 128), (1, 2, 256, 128), 8, torch.bfloat16)
+    ab = (0.5 * torch.randn(1, 2, 256, 256, device="cuda")).requires_grad_(True)
+    qg = q.clone().requires_grad_(True)
+    o = fa.flex_attention(qg, k, v, ab, causal=True, sm_scale=0.09)
+    o.backward(do)
+    assert ab.grad is not None and ab.grad.shape == ab.shape and qg.grad is not None
+    # strictly upper-triangular pairs are masked: no gradient reaches the bias there
+    assert float(ab.grad[0, 0].triu(1).abs().max()) == 0.0 and float(ab.grad.abs().max()) > 0.0
+    with pytest.raises(FlexAttnError):
+        fa._flex_attention_impl(q, k, v, ab.detach(), None, True, True, 0.09, 1, 128, 128, 128, False, None, None, None,
+                                backend="tcgen05")
