@@ -22,6 +22,7 @@
 //
 // Tensor memory: S0, S1, S2 (3 x 128 columns) + O (D columns) = 512 for D = 128.  Shared memory: 2 Q + 2 K +
 // 2 V tiles (192 KB for D = 128).
+#include "sched.cuh"
 #include "sm100.cuh"
 
 #ifdef FLEXATTN_TRACE
@@ -52,68 +53,6 @@ struct PipeSmem {
   float pmax[2][2][kTile];  // [tile parity][column half][row]
   float lsum[2][kTile];     // [column half][row]
   int32_t doc[2][kTile];
-};
-
-// A CTA's walk over its work items.  The heads of a batch row are taken in groups small enough for the K and V of a
-// whole group to stay in L2 (every q tile of a slice re-reads them); inside a group the items follow the mask map's
-// work order of the q tiles (most kv tiles first), head index fastest.  The resulting list is dealt to the CTAs in
-// rounds that alternate direction (CTA c takes entry c of an even round and entry G-1-c of an odd one), which evens
-// out the work of a sorted list.  Tile order and mask-map row of the next item are fetched one item ahead.
-struct ItemCursor {
-  const DevParams& P;
-  int total, per_row, group, full_groups;
-  int round, w;      // current round and item; valid while w < total
-  int4 rm, rm_next;  // mask-map rows {first kv tile, end kv tile, first full, end full} of this item and the next
-  int bh_, qt_, bh_next, qt_next;
-  __device__ __forceinline__ int item_of(int r) const {
-    const int G = (int)gridDim.x, c = (int)blockIdx.x;
-    return r * G + ((r & 1) ? G - 1 - c : c);
-  }
-  __device__ __forceinline__ int4 fetch(int item, int& bh, int& qt) const {
-    const int b = item / per_row, r = item - b * per_row;
-    int gi = r / (group * P.n_qt), width = group;
-    if (gi >= full_groups) {  // the last, smaller group of the batch row
-      gi = full_groups;
-      width = P.heads - full_groups * group;
-    }
-    const int r2 = r - gi * group * P.n_qt;
-    const int rank = r2 / width;
-    bh = b * P.heads + gi * group + (r2 - rank * width);
-    const size_t row = (size_t)(P.map_rows > 1 ? b : 0) * P.n_qt;
-    qt = __ldg(&P.order[row + rank]);
-    return __ldg(&P.row_map[row + qt]);
-  }
-  __device__ __forceinline__ ItemCursor(const DevParams& p) : P(p) {
-    per_row = p.heads * p.n_qt;
-    total = p.batch * per_row;
-    // K + V of one slice: 2 * seq_k * head_dim * 2 bytes; keep about 48 MB of them live
-    const long long slice_bytes = 4ll * p.seq_k * p.head_dim;
-    group = (int)max(1ll, min((long long)p.heads, (48ll << 20) / slice_bytes));
-    full_groups = p.heads / group;
-    round = 0;
-    w = item_of(0);
-    rm = rm_next = make_int4(0, 0, 0, 0);
-    bh_ = qt_ = bh_next = qt_next = 0;
-    if (w < total) rm = fetch(w, bh_, qt_);
-    if (item_of(1) < total) rm_next = fetch(item_of(1), bh_next, qt_next);
-  }
-  __device__ __forceinline__ bool valid() const { return w < total; }
-  __device__ __forceinline__ int tiles() const { return rm.y - rm.x; }
-  __device__ __forceinline__ int bh() const { return bh_; }
-  __device__ __forceinline__ int qt() const { return qt_; }
-  __device__ __forceinline__ void next() {
-    ++round;
-    w = item_of(round);
-    rm = rm_next;
-    bh_ = bh_next;
-    qt_ = qt_next;
-    const int nxt = item_of(round + 1);
-    if (nxt < total) rm_next = fetch(nxt, bh_next, qt_next);
-  }
-  // skip items without any kv tile (the producers and the MMA issuer have nothing to do for them)
-  __device__ __forceinline__ void skip_empty() {
-    while (valid() && tiles() <= 0) next();
-  }
 };
 
 // x: this thread's 64 raw scores (columns c_base .. c_base+63 of the tile) -> log2-domain logits in place;
@@ -553,19 +492,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
   }
-}
-
-// Number of SMs of the current device (queried once per device).
-int sm_count() {
-  static int cached[64] = {0};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
-    cached[dev] = n;
-  }
-  return cached[dev];
 }
 
 template <int D, int SK, int MK>
