@@ -145,13 +145,13 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (tid == 0) {
     ptx::mbar_init(&sh->bar_q, 1);
-    ptx::mbar_init(&sh->bar_qtm, 256);
+    ptx::mbar_init(&sh->bar_qtm, 8);  // one arrival per warp of the two warpgroups, here and below
     ptx::mbar_init(&sh->bar_kv[0], 1);
     ptx::mbar_init(&sh->bar_kv[1], 1);
     ptx::mbar_init(&sh->bar_kv[2], 1);
     ptx::mbar_init(&sh->bar_sdp, 1);
-    ptx::mbar_init(&sh->bar_ld, 256);
-    ptx::mbar_init(&sh->bar_ds, 256);
+    ptx::mbar_init(&sh->bar_ld, 8);
+    ptx::mbar_init(&sh->bar_ds, 8);
     ptx::mbar_init(&sh->bar_dq, 1);
     ptx::fence_barrier_init();
   }
@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
       }
-      ptx::mbar_arrive(&sh->bar_qtm);
+      ptx::mbar_arrive_warp(&sh->bar_qtm);
       FA_MARK(3);
     }
 
@@ -347,7 +347,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::tmem_ld_acquire(pr[0]);
       ptx::tmem_ld_acquire(pr[1]);
       ptx::tc_fence_before();
-      ptx::mbar_arrive(&sh->bar_ld);  // S / dP columns may be overwritten by the next tile's MMAs
+      ptx::mbar_arrive_warp(&sh->bar_ld);  // S / dP columns may be overwritten by the next tile's MMAs
       if (tid == 0) FA_TRACE(9);
       uint32_t pk[32];
       const float abase = slope2 * (float)(j0 - i);
@@ -368,7 +368,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         *reinterpret_cast<uint4*>(ds_row + ((jc ^ (row & 7)) << 4)) = v4;
       }
       ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the MMA's shared-memory reads
-      ptx::mbar_arrive(&sh->bar_ds);
+      ptx::mbar_arrive_warp(&sh->bar_ds);
       if (tid == 0) FA_TRACE(11);
     }
 
