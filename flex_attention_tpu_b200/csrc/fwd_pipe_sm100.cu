@@ -188,9 +188,17 @@ __global__ void __launch_bounds__(kThreads, 1)
                              (first + t) * kTile, bh);
         }
       }
-      if (ok) {  // end of the list: one more completion of the Q barrier, carrying the terminator
-        sh->item_tiles[qi & 7] = -1;
-        ptx::mbar_arrive(&sh->bar_q[qi & 1]);
+      if (ok) {
+        // End of the list: one more completion of the Q barrier, carrying the terminator.  Like a real item it has to
+        // wait for the barrier's previous phase (the Q tile of item qi-2) to be over - its bytes landed and consumed -
+        // before arriving on it again: an arrive into a phase that still expects bytes would corrupt it.
+        if (qi >= 2) ok = ptx::mbar_wait(&sh->bar_qfree[qi & 1], ((qi - 2) >> 1) & 1);
+        if (ok) {
+          sh->item_tiles[qi & 7] = -1;
+          ptx::mbar_arrive(&sh->bar_q[qi & 1]);
+        } else {
+          fail_at = 24;
+        }
       }
       if (!ok) give_up(abort_flag, P.status, 4, fail_at);
     }

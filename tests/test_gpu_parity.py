@@ -126,3 +126,20 @@ def test_tensor_core_matches_simt_on_long_rows():
     for n in ("o", "dq", "dk", "dv"):
         e = errors(a[n], b[n].float().cpu().numpy(), 2 * TOL[torch.bfloat16]["round"])   # both sides stored in bf16
         assert e["max_abs_excess"] <= TOL[torch.bfloat16]["abs"] and e["max_rel"] <= TOL[torch.bfloat16]["rel"], (n, e)
+
+
+@pytest.mark.parametrize("S", [128, 256, 384])
+def test_persistent_forward_with_many_short_items(S, monkeypatch):
+    """The persistent forward walks several work items per CTA as one kv-tile stream, with Q K^T running three tiles
+    (here: up to three ITEMS) ahead of the softmax.  Many one- to three-tile items per CTA exercise every item
+    boundary hazard: Q stage reuse, the first P V of an item after the previous item's epilogue, the end of the list."""
+    monkeypatch.setenv("FLEXATTN_FWD_VARIANT", "2")
+    fa = _fa()
+    (q, k, v, do), _ = make_qkvdo((5, 96, S, 64), (5, 96, S, 64), 600 + S, torch.bfloat16)
+    sm = 0.125
+    a = run_hot_path(fa, q, k, v, do, sm_scale=sm, mask_kind="causal", backend="tcgen05")
+    b = run_hot_path(fa, q, k, v, do, sm_scale=sm, mask_kind="causal", backend="simt")
+    for n in ("o", "dq", "dk", "dv"):
+        e = errors(a[n], b[n].float().cpu().numpy(), 2 * TOL[torch.bfloat16]["round"])   # both sides stored in bf16
+        assert e["max_abs_excess"] <= TOL[torch.bfloat16]["abs"] and e["max_rel"] <= TOL[torch.bfloat16]["rel"], (n, e)
+    assert float((a["l"] / b["l"] - 1).abs().max()) <= 2e-2
