@@ -30,7 +30,7 @@ constexpr int32_t kMapMagic = 0x464c5841;  // "FLXA"
 
 struct MapLayout {
   int n_qt, n_kt, rows, n_t;
-  size_t off_row, off_col, off_doc, off_order, bytes;
+  size_t off_row, off_col, off_doc, off_order, off_order_rm, bytes;
 };
 
 __host__ __device__ inline MapLayout map_layout(int batch, int seq_q, int seq_k, int mask_kind) {
@@ -46,7 +46,9 @@ __host__ __device__ inline MapLayout map_layout(int batch, int seq_q, int seq_k,
   // q tiles of every map row ordered by their number of kv tiles, largest first (work order of the persistent
   // forward kernel)
   L.off_order = (L.off_doc + doc + 15) & ~(size_t)15;
-  L.bytes = (L.off_order + sizeof(int32_t) * (size_t)L.rows * L.n_qt + 255) & ~(size_t)255;
+  // ... and the row-map entries in that order (so that walking the order needs no dependent load)
+  L.off_order_rm = (L.off_order + sizeof(int32_t) * (size_t)L.rows * L.n_qt + 15) & ~(size_t)15;
+  L.bytes = (L.off_order_rm + sizeof(int4) * (size_t)L.rows * L.n_qt + 255) & ~(size_t)255;
   return L;
 }
 
@@ -70,6 +72,7 @@ struct DevParams {
   const int4* row_map;  // [rows][n_qt]
   const int4* col_map;  // [rows][n_kt]
   const int32_t* order;  // [rows][n_qt]: q tiles by decreasing number of kv tiles
+  const int4* order_rm;  // [rows][n_qt]: row_map entry of order[i]
   int32_t* status;
   long long* trace;  // per-phase cycle stamps of one CTA; only written by builds with FLEXATTN_TRACE
   int batch, heads, seq_q, seq_k, head_dim;

@@ -451,10 +451,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_pv[sb == 0 ? kSBufs - 1 : sb - 1], sb == 0 ? sph ^ 1u : sph));
         if (!ok) fail_at = 12;
       }
+      if (tid == 0) FA_TRACE_T(T - 1, 13);
       sh->lsum[half][row] = l;
       ptx::named_bar_sync(1, 256);
       l = sh->lsum[0][row] + sh->lsum[1][row];
       ptx::named_bar_sync(3, 256);  // both halves have read lsum before the next item overwrites it
+      if (tid == 0) FA_TRACE_T(T - 1, 14);
       if (ok) {
         const float inv_l = l > 0.f ? ptx::kRoundUp / l : 0.f;  // l sums the pre-scaled probabilities
         const size_t grow = (size_t)bh * P.seq_q + i;
@@ -489,6 +491,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           P.m[grow] = m_true * kLn2;
         }
       }
+      if (tid == 0) FA_TRACE_T(T - 1, 15);
     }
     if (!ok && lane == 0) give_up(abort_flag, P.status, 4, fail_at);
   }

@@ -117,10 +117,12 @@ __global__ void mask_map_kernel(MapHeader hdr, MapHeader* __restrict__ hdr_out, 
 
 // Work order of the q tiles of one map row: by decreasing number of kv tiles (counting sort; ties by decreasing
 // tile index, so the result is deterministic).  One CTA per map row; hist has n_kt + 2 entries.
-__global__ void order_kernel(const int4* __restrict__ row_map, int32_t* __restrict__ order, int n_qt, int n_kt) {
+__global__ void order_kernel(const int4* __restrict__ row_map, int32_t* __restrict__ order, int4* __restrict__ order_rm,
+                             int n_qt, int n_kt) {
   extern __shared__ int hist[];
   const int4* rm = row_map + (size_t)blockIdx.x * n_qt;
   int32_t* ord = order + (size_t)blockIdx.x * n_qt;
+  int4* ord_rm = order_rm + (size_t)blockIdx.x * n_qt;
   for (int i = threadIdx.x; i < n_kt + 2; i += blockDim.x) hist[i] = 0;
   __syncthreads();
   for (int t = threadIdx.x; t < n_qt; t += blockDim.x) atomicAdd(&hist[rm[t].y - rm[t].x], 1);
@@ -134,6 +136,8 @@ __global__ void order_kernel(const int4* __restrict__ row_map, int32_t* __restri
     }
     for (int t = n_qt - 1; t >= 0; --t) ord[hist[rm[t].y - rm[t].x]++] = t;
   }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_qt; i += blockDim.x) ord_rm[i] = rm[ord[i]];
 }
 
 }  // namespace
@@ -164,7 +168,8 @@ cudaError_t launch_mask_map(cudaStream_t st, const FlexAttnParams& p) {
   const size_t hist_bytes = sizeof(int) * (size_t)(L.n_kt + 2);
   if (hist_bytes > 48 * 1024) return cudaErrorInvalidValue;  // more than 12 286 kv tiles (1.5 M keys)
   order_kernel<<<L.rows, 256, hist_bytes, st>>>(reinterpret_cast<const int4*>(ws + L.off_row),
-                                                 reinterpret_cast<int32_t*>(ws + L.off_order), L.n_qt, L.n_kt);
+                                                 reinterpret_cast<int32_t*>(ws + L.off_order),
+                                                 reinterpret_cast<int4*>(ws + L.off_order_rm), L.n_qt, L.n_kt);
   return cudaGetLastError();
 }
 

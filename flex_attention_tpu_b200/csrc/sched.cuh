@@ -31,7 +31,7 @@ struct ItemCursor {
     bh = b * P.heads + gi * group + (r2 - rank * width);
     const size_t row = (size_t)(P.map_rows > 1 ? b : 0) * P.n_qt;
     qt = __ldg(&P.order[row + rank]);
-    return __ldg(&P.row_map[row + qt]);
+    return __ldg(&P.order_rm[row + rank]);  // the row-map entry of that q tile: two independent loads
   }
   __device__ __forceinline__ ItemCursor(const DevParams& p) : P(p) {
     per_row = p.heads * p.n_qt;

@@ -143,3 +143,15 @@ def test_persistent_forward_with_many_short_items(S, monkeypatch):
         e = errors(a[n], b[n].float().cpu().numpy(), 2 * TOL[torch.bfloat16]["round"])   # both sides stored in bf16
         assert e["max_abs_excess"] <= TOL[torch.bfloat16]["abs"] and e["max_rel"] <= TOL[torch.bfloat16]["rel"], (n, e)
     assert float((a["l"] / b["l"] - 1).abs().max()) <= 2e-2
+
+
+def test_persistent_forward_rectangular_with_many_items(monkeypatch):
+    """Sq != Sk, no mask, several items per CTA (every item has the same five kv tiles)."""
+    monkeypatch.setenv("FLEXATTN_FWD_VARIANT", "2")
+    fa = _fa()
+    (q, k, v, do), _ = make_qkvdo((4, 64, 256, 128), (4, 64, 640, 128), 611, torch.bfloat16)
+    a = run_hot_path(fa, q, k, v, do, sm_scale=0.09, mask_kind="none", backend="tcgen05")
+    b = run_hot_path(fa, q, k, v, do, sm_scale=0.09, mask_kind="none", backend="simt")
+    for n in ("o", "dq", "dk", "dv"):
+        e = errors(a[n], b[n].float().cpu().numpy(), 2 * TOL[torch.bfloat16]["round"])   # both sides stored in bf16
+        assert e["max_abs_excess"] <= TOL[torch.bfloat16]["abs"] and e["max_rel"] <= TOL[torch.bfloat16]["rel"], (n, e)
