@@ -9,7 +9,8 @@
 //
 //   warp 8, lane 0 : MMA issuer.  S[T % 3] = Q K[T]^T runs up to three kv tiles ahead of the softmax;
 //                    O += P[T] V[T] is issued as soon as the softmax has written P[T] over S[T % 3].
-//   warp 9, lane 0 : TMA producer for Q (two stages, one per item in flight) and K (two-stage ring).
+//   warp 9, lane 0 : TMA producer for Q (one buffer: the next item's Q is loaded as soon as the last Q K^T of the
+//                    current item has run, three tiles before its softmax ends) and K (two-stage ring).
 //   warp 10, lane 0: TMA producer for V (two-stage ring).  Each ring stage is refilled as soon as the MMA that
 //                    read it has completed (tcgen05.commit -> mbarrier).
 //   warps 0..7     : softmax, two warpgroups.  Threads t and t + 128 share query row t (= TMEM lane t)
@@ -20,8 +21,8 @@
 //                    to the next item; the first P V of that item is issued only after they have written
 //                    its first P, i.e. after they are done reading the previous O.
 //
-// Tensor memory: S0, S1, S2 (3 x 128 columns) + O (D columns) = 512 for D = 128.  Shared memory: 2 Q + 2 K +
-// 2 V tiles (192 KB for D = 128).
+// Tensor memory: S0, S1, S2 (3 x 128 columns) + O (D columns) = 512 for D = 128.  Shared memory: Q, an output
+// staging tile, 2 K and 2 V tiles (192 KB for D = 128).
 #include "sched.cuh"
 #include "sm100.cuh"
 
@@ -47,7 +48,7 @@ constexpr int kSBufs = 3;
 constexpr float kLazyRescale = 8.0f;  // log2 units
 
 struct PipeSmem {
-  uint64_t bar_q[2], bar_qfree[2], bar_k[2], bar_v[2], bar_kfree[2], bar_s[kSBufs], bar_p[kSBufs], bar_pv[kSBufs];
+  uint64_t bar_q, bar_qfree, bar_k[2], bar_v[2], bar_kfree[2], bar_s[kSBufs], bar_p[kSBufs], bar_pv[kSBufs];
   uint32_t tmem_base;
   int32_t item_tiles[8];  // kv tiles of the CTA's non-empty items (ring; -1 ends the list), producer -> MMA issuer
   float pmax[2][2][kTile];  // [tile parity][column half][row]
@@ -107,7 +108,8 @@ __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, in
 template <int D, int SK, int MK>
 __global__ void __launch_bounds__(kThreads, 1)
     fwd_pipe_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                          const __grid_constant__ CUtensorMap tm_v, const DevParams P, int* abort_flag) {
+                          const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                          const DevParams P, int* abort_flag) {
   constexpr int kPanels = D / 64;
   constexpr uint32_t kTileBytes = kPanels * ptx::kPanelBytes;
   constexpr uint32_t kTmemCols = 512;
@@ -115,7 +117,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;                   // two stages
+  uint8_t* sQ = smem;                   // the Q tile of the item whose Q K^T MMAs are being issued
+  uint8_t* sO = smem + kTileBytes;      // staging of an item's output tile for its bulk store
   uint8_t* sK = smem + 2 * kTileBytes;  // two stages
   uint8_t* sV = smem + 4 * kTileBytes;  // two stages
   PipeSmem* sh = reinterpret_cast<PipeSmem*>(smem + 6 * kTileBytes);
@@ -125,9 +128,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (*reinterpret_cast<volatile int*>(abort_flag) != 0) return;
 
   if (tid == 0) {
+    ptx::mbar_init(&sh->bar_q, 1);
+    ptx::mbar_init(&sh->bar_qfree, 1);
     for (int s = 0; s < 2; ++s) {
-      ptx::mbar_init(&sh->bar_q[s], 1);
-      ptx::mbar_init(&sh->bar_qfree[s], 1);
       ptx::mbar_init(&sh->bar_k[s], 1);
       ptx::mbar_init(&sh->bar_v[s], 1);
       ptx::mbar_init(&sh->bar_kfree[s], 1);
@@ -166,16 +169,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         it.skip_empty();
         if (!it.valid()) break;
         const int bh = it.bh(), first = it.rm.x, N = it.tiles();
-        if (qi >= 2) {  // the stage held the Q tile of item qi-2: all of its Q K^T MMAs must have completed
-          ok = ptx::mbar_wait(&sh->bar_qfree[qi & 1], ((qi - 2) >> 1) & 1);
+        if (qi >= 1) {  // the buffer holds the Q tile of the previous item: all of its Q K^T MMAs must have completed
+          ok = ptx::mbar_wait(&sh->bar_qfree, (qi - 1) & 1);
           if (!ok) { fail_at = 20; break; }
         }
         sh->item_tiles[qi & 7] = N;  // read by the MMA issuer after it has waited on bar_q (release / acquire)
-        ptx::mbar_arrive_expect_tx(&sh->bar_q[qi & 1], kTileBytes);
+        ptx::mbar_arrive_expect_tx(&sh->bar_q, kTileBytes);
 #pragma unroll
         for (int p = 0; p < kPanels; ++p)
-          ptx::tma_load_3d(sQ + (qi & 1) * kTileBytes + p * ptx::kPanelBytes, &tm_q, &sh->bar_q[qi & 1], p * 64,
-                           it.qt() * kTile, bh);
+          ptx::tma_load_3d(sQ + p * ptx::kPanelBytes, &tm_q, &sh->bar_q, p * 64, it.qt() * kTile, bh);
         for (int t = 0; t < N; ++t, ++T) {
           if (T >= 2) {  // K[T] replaces K[T-2], read by Q K^T of tile T-2
             ok = ptx::mbar_wait(&sh->bar_kfree[T & 1], ((T - 2) >> 1) & 1);
@@ -190,12 +192,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (ok) {
         // End of the list: one more completion of the Q barrier, carrying the terminator.  Like a real item it has to
-        // wait for the barrier's previous phase (the Q tile of item qi-2) to be over - its bytes landed and consumed -
+        // wait for the barrier's previous phase (the Q tile of the previous item) to be over - its bytes landed and consumed -
         // before arriving on it again: an arrive into a phase that still expects bytes would corrupt it.
-        if (qi >= 2) ok = ptx::mbar_wait(&sh->bar_qfree[qi & 1], ((qi - 2) >> 1) & 1);
+        if (qi >= 1) ok = ptx::mbar_wait(&sh->bar_qfree, (qi - 1) & 1);
         if (ok) {
           sh->item_tiles[qi & 7] = -1;
-          ptx::mbar_arrive(&sh->bar_q[qi & 1]);
+          ptx::mbar_arrive(&sh->bar_q);
         } else {
           fail_at = 24;
         }
@@ -249,10 +251,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       int pT = 0, pn = 0, pqi = 0, pN = 0;  // P V position
       bool q_end = false;
       uint32_t qsb = 0, psb = 0, psph = 0;
-      const ptx::DescBase bQ0 = ptx::base_kmajor(aQ), bQ1 = ptx::base_kmajor(aQ + kTileBytes);
+      const ptx::DescBase bQ = ptx::base_kmajor(aQ);
       auto issue_qk = [&]() {  // one tile at the Q K^T position, then advance it
         if (qn == 0) {
-          ok = ptx::mbar_wait(&sh->bar_q[qqi & 1], (qqi >> 1) & 1);
+          ok = ptx::mbar_wait(&sh->bar_q, qqi & 1);
           if (!ok) { fail_at = 2; return; }
           qN = sh->item_tiles[qqi & 7];
           if (qN < 0) { q_end = true; return; }
@@ -260,18 +262,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = ptx::mbar_wait(&sh->bar_k[qT & 1], (qT >> 1) & 1);
         if (!ok) { fail_at = 3; return; }
         ptx::tc_fence_after();
-        const ptx::DescBase bq = (qqi & 1) ? bQ1 : bQ0;
         const ptx::DescBase bk = (qT & 1) ? bK1 : bK0;
         const uint32_t dS = tmem + qsb * 128u;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          ptx::mma_ss(dS, ptx::desc_at(bq, ptx::koff_kmajor(kk)), ptx::desc_at(bk, ptx::koff_kmajor(kk)), idesc_qk, kk > 0);
+          ptx::mma_ss(dS, ptx::desc_at(bQ, ptx::koff_kmajor(kk)), ptx::desc_at(bk, ptx::koff_kmajor(kk)), idesc_qk, kk > 0);
         ptx::mma_commit(&sh->bar_s[qsb]);
         ptx::mma_commit(&sh->bar_kfree[qT & 1]);
         ++qT;
         if (++qsb == kSBufs) qsb = 0;
         if (++qn == qN) {
-          ptx::mma_commit(&sh->bar_qfree[qqi & 1]);
+          ptx::mma_commit(&sh->bar_qfree);
           qn = 0;
           ++qqi;
         }
@@ -316,6 +317,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool ok = true;
     int fail_at = 0;
     int T = 0;  // stream index of the next kv tile
+    bool o_pending = false;  // thread 0: a bulk store out of the staging tile has been issued and not yet waited for
     int sb = 0;          // T % 3: score buffer of that tile
     uint32_t sph = 0;    // (T / 3) & 1: phase of its barriers
 
@@ -452,28 +454,30 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!ok) fail_at = 12;
       }
       if (tid == 0) FA_TRACE_T(T - 1, 13);
+      if (tid == 0 && o_pending) {  // the previous item's store has read the staging tile (long ago, normally)
+        ptx::tma_store_wait_read();
+        o_pending = false;
+      }
       sh->lsum[half][row] = l;
       ptx::named_bar_sync(1, 256);
       l = sh->lsum[0][row] + sh->lsum[1][row];
       ptx::named_bar_sync(3, 256);  // both halves have read lsum before the next item overwrites it
       if (tid == 0) FA_TRACE_T(T - 1, 14);
-      if (ok) {
-        const float inv_l = l > 0.f ? ptx::kRoundUp / l : 0.f;  // l sums the pre-scaled probabilities
-        const size_t grow = (size_t)bh * P.seq_q + i;
-        if (N > 0) ptx::tc_fence_after();
-        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(P.o) + grow * D;
+      const float inv_l = l > 0.f ? ptx::kRoundUp / l : 0.f;  // l sums the pre-scaled probabilities
+      const size_t grow = (size_t)bh * P.seq_q + i;
+      if (N > 0) {
+        // O / l as bf16 into the staging tile in the TMA (128-byte swizzle) layout, then one bulk tensor store per
+        // 64-column panel; rows past seq_q are clipped by the tensor map.  (Storing from registers, one 256-byte row
+        // per thread, touched 32 different lines per instruction and cost 3400 cycles per item.)
+        if (ok) {
+          ptx::tc_fence_after();
+          uint8_t* stage_row = sO + row * 128;
 #pragma unroll 1
-        for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
-          uint32_t r[32];
-          if (N > 0) {
+          for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
+            uint32_t r[32];
             ptx::tmem_ld32(lane_base + kColO + c0, r);
             ptx::tmem_wait_ld();
             ptx::tmem_ld_acquire(r);
-          } else {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) r[c] = 0u;
-          }
-          if (i < P.seq_q) {
 #pragma unroll
             for (int c = 0; c < 32; c += 8) {
               uint4 v4;
@@ -481,18 +485,32 @@ __global__ void __launch_bounds__(kThreads, 1)
               v4.y = ptx::pack_bf16(__uint_as_float(r[c + 2]) * inv_l, __uint_as_float(r[c + 3]) * inv_l);
               v4.z = ptx::pack_bf16(__uint_as_float(r[c + 4]) * inv_l, __uint_as_float(r[c + 5]) * inv_l);
               v4.w = ptx::pack_bf16(__uint_as_float(r[c + 6]) * inv_l, __uint_as_float(r[c + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow + c0 + c) = v4;
+              const int col = c0 + c, panel = col >> 6, chunk = (col & 63) >> 3;
+              *reinterpret_cast<uint4*>(stage_row + panel * ptx::kPanelBytes + ((chunk ^ (row & 7)) << 4)) = v4;
             }
           }
+          ptx::tc_fence_before();
+          ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the bulk store
         }
-        if (N > 0) ptx::tc_fence_before();
-        if (half == 0 && i < P.seq_q) {
-          P.l[grow] = l * ptx::ex2(m_ref - m_true) * ptx::kRoundInv;
-          P.m[grow] = m_true * kLn2;
+        ptx::named_bar_sync(2, 256);
+        if (ok && tid == 0) {
+#pragma unroll
+          for (int p = 0; p < kPanels; ++p) ptx::tma_store_3d(&tm_o, sO + p * ptx::kPanelBytes, p * 64, qt * kTile, bh);
+          ptx::tma_store_commit();
+          o_pending = true;
         }
+      } else if (ok && i < P.seq_q) {  // an item without any kv tile: zeros, written directly
+        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(P.o) + grow * D;
+        for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 8)
+          *reinterpret_cast<uint4*>(orow + c0) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      if (ok && half == 0 && i < P.seq_q) {
+        P.l[grow] = l * ptx::ex2(m_ref - m_true) * ptx::kRoundInv;
+        P.m[grow] = m_true * kLn2;
       }
       if (tid == 0) FA_TRACE_T(T - 1, 15);
     }
+    if (tid == 0 && o_pending) ptx::tma_store_wait_read();  // the staging tile must outlive the last store's reads
     if (!ok && lane == 0) give_up(abort_flag, P.status, 4, fail_at);
   }
 
@@ -507,7 +525,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 template <int D, int SK, int MK>
 int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const CUtensorMap& tk,
-               const CUtensorMap& tv, int* abort_flag) {
+               const CUtensorMap& tv, const CUtensorMap& to, int* abort_flag) {
   constexpr size_t need = 6 * (D / 64) * ptx::kPanelBytes + sizeof(PipeSmem) + 1024;
   // 512 TMEM columns per CTA: never let two CTAs share an SM (the second would spin in tcgen05.alloc)
   constexpr size_t smem = need > 120 * 1024 ? need : 120 * 1024;
@@ -523,32 +541,32 @@ int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const
   const int sms = sm_count();
   if (sms <= 0) return FLEXATTN_ERR_CUDA;
   dim3 grid((unsigned)(items < sms ? items : sms));
-  kern<<<grid, kThreads, smem, st>>>(tq, tk, tv, d, abort_flag);
+  kern<<<grid, kThreads, smem, st>>>(tq, tk, tv, to, d, abort_flag);
   return cudaGetLastError() == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;
 }
 
 template <int D, int SK>
 int launch_mask(cudaStream_t st, const DevParams& d, int mask, const CUtensorMap& tq, const CUtensorMap& tk,
-                const CUtensorMap& tv, int* af) {
+                const CUtensorMap& tv, const CUtensorMap& to, int* af) {
   switch (mask) {
-    case FLEXATTN_MASK_NONE: return launch_one<D, SK, FLEXATTN_MASK_NONE>(st, d, tq, tk, tv, af);
-    case FLEXATTN_MASK_CAUSAL: return launch_one<D, SK, FLEXATTN_MASK_CAUSAL>(st, d, tq, tk, tv, af);
-    case FLEXATTN_MASK_SLIDING_WINDOW: return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW>(st, d, tq, tk, tv, af);
+    case FLEXATTN_MASK_NONE: return launch_one<D, SK, FLEXATTN_MASK_NONE>(st, d, tq, tk, tv, to, af);
+    case FLEXATTN_MASK_CAUSAL: return launch_one<D, SK, FLEXATTN_MASK_CAUSAL>(st, d, tq, tk, tv, to, af);
+    case FLEXATTN_MASK_SLIDING_WINDOW: return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW>(st, d, tq, tk, tv, to, af);
     case FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL:
-      return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL>(st, d, tq, tk, tv, af);
-    case FLEXATTN_MASK_DOCUMENT: return launch_one<D, SK, FLEXATTN_MASK_DOCUMENT>(st, d, tq, tk, tv, af);
-    case FLEXATTN_MASK_S2: return launch_one<D, SK, FLEXATTN_MASK_S2>(st, d, tq, tk, tv, af);
+      return launch_one<D, SK, FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL>(st, d, tq, tk, tv, to, af);
+    case FLEXATTN_MASK_DOCUMENT: return launch_one<D, SK, FLEXATTN_MASK_DOCUMENT>(st, d, tq, tk, tv, to, af);
+    case FLEXATTN_MASK_S2: return launch_one<D, SK, FLEXATTN_MASK_S2>(st, d, tq, tk, tv, to, af);
     default: return FLEXATTN_ERR_UNSUPPORTED_MOD;
   }
 }
 
 template <int D>
 int launch_score(cudaStream_t st, const DevParams& d, int score, int mask, const CUtensorMap& tq,
-                 const CUtensorMap& tk, const CUtensorMap& tv, int* af) {
+                 const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to, int* af) {
   switch (score) {
-    case FLEXATTN_SCORE_NONE: return launch_mask<D, FLEXATTN_SCORE_NONE>(st, d, mask, tq, tk, tv, af);
-    case FLEXATTN_SCORE_ALIBI: return launch_mask<D, FLEXATTN_SCORE_ALIBI>(st, d, mask, tq, tk, tv, af);
-    case FLEXATTN_SCORE_SOFTCAP: return launch_mask<D, FLEXATTN_SCORE_SOFTCAP>(st, d, mask, tq, tk, tv, af);
+    case FLEXATTN_SCORE_NONE: return launch_mask<D, FLEXATTN_SCORE_NONE>(st, d, mask, tq, tk, tv, to, af);
+    case FLEXATTN_SCORE_ALIBI: return launch_mask<D, FLEXATTN_SCORE_ALIBI>(st, d, mask, tq, tk, tv, to, af);
+    case FLEXATTN_SCORE_SOFTCAP: return launch_mask<D, FLEXATTN_SCORE_SOFTCAP>(st, d, mask, tq, tk, tv, to, af);
     default: return FLEXATTN_ERR_UNSUPPORTED_MOD;
   }
 }
@@ -558,7 +576,7 @@ int launch_score(cudaStream_t st, const DevParams& d, int score, int mask, const
 int launch_sm100_fwd_pipe(cudaStream_t st, const DevParams& d, int score, int mask) {
   int* af = abort_flag_ptr();
   if (af == nullptr) return FLEXATTN_ERR_CUDA;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   const int slices = d.batch * d.heads;
   int e = make_tile_map(&tq, d.q, slices, d.seq_q, d.head_dim);
   if (e) return e;
@@ -566,8 +584,10 @@ int launch_sm100_fwd_pipe(cudaStream_t st, const DevParams& d, int score, int ma
   if (e) return e;
   e = make_tile_map(&tv, d.v, slices, d.seq_k, d.head_dim);
   if (e) return e;
-  if (d.head_dim == 128) return launch_score<128>(st, d, score, mask, tq, tk, tv, af);
-  if (d.head_dim == 64) return launch_score<64>(st, d, score, mask, tq, tk, tv, af);
+  e = make_tile_map(&to, d.o, slices, d.seq_q, d.head_dim);
+  if (e) return e;
+  if (d.head_dim == 128) return launch_score<128>(st, d, score, mask, tq, tk, tv, to, af);
+  if (d.head_dim == 64) return launch_score<64>(st, d, score, mask, tq, tk, tv, to, af);
   return FLEXATTN_ERR_UNSUPPORTED_HEAD_DIM;
 }
 
