@@ -8,7 +8,6 @@
 namespace flexattn {
 namespace {
 
-constexpr int kPipeMinSeqK = 1024;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -153,13 +152,7 @@ int flexattn_fwd(void* stream, const FlexAttnParams* p) {
   DevParams d = make_dev(p);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (tc) {
-    // Two forward kernels: the pipelined one (three score tiles in flight, one CTA per SM) wins once a row
-    // has enough kv tiles to amortise its longer prologue; FLEXATTN_FWD_VARIANT=1|2 forces one (tests).
-    int variant = 0;
-    if (const char* env = getenv("FLEXATTN_FWD_VARIANT")) variant = atoi(env);
-    if (variant < 1 || variant > 2) variant = p->seq_k >= kPipeMinSeqK ? 2 : 1;
-    return variant == 2 ? launch_sm100_fwd_pipe(st, d, p->score_kind, p->mask_kind)
-                        : launch_sm100_fwd(st, d, p->score_kind, p->mask_kind);
+    return launch_sm100_fwd_pipe(st, d, p->score_kind, p->mask_kind);
   }
   return launch_simt_fwd(st, d, p->dtype, p->score_kind, p->mask_kind) == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;
 }

@@ -1,6 +1,7 @@
 // Forward flex attention, persistent software-pipelined kernel (sm_100a).
 //
-// Same math and interface as fwd_sm100.cu (reference: flex_attention_kernel.py:196-327).  One CTA per SM stays
+// Replaces the reference's Pallas forward kernel (flex_attention_kernel.py:196-327): online softmax in the log2
+// domain over 128 x 128 score tiles, masks evaluated only on partial tiles.  One CTA per SM stays
 // resident and walks a list of work items (q tile, batch*head), heaviest q tiles first, item w going to CTA
 // w mod gridDim.x.  Inside a CTA the kv tiles of all its items form ONE stream, numbered T = 0, 1, 2 ...: the
 // K/V rings, the three score buffers and every barrier phase are indexed by T, so the loads and the Q K^T MMAs

@@ -86,22 +86,16 @@ def test_simt_bfloat16(mask_kind, score_kind):
     _case(mask_kind, score_kind, torch.bfloat16, 1, 2, 300, 300, 128, 104, "simt")
 
 
-@pytest.mark.parametrize("fwd_variant", [1, 2])
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("score_kind", ["none", "alibi", "softcap"])
 @pytest.mark.parametrize("mask_kind", sorted(MASKS))
-def test_tensor_core_bfloat16(mask_kind, score_kind, D, fwd_variant, monkeypatch):
-    """The tcgen05 kernels: every mask x score functor, both head dims, ragged sequence (not a tile multiple),
-    and both forward kernels (1 = one score tile in flight, 2 = pipelined; chosen by sequence length in
-    normal use, forced here)."""
-    monkeypatch.setenv("FLEXATTN_FWD_VARIANT", str(fwd_variant))
+def test_tensor_core_bfloat16(mask_kind, score_kind, D):
+    """The tcgen05 kernels: every mask x score functor, both head dims, ragged sequence (not a tile multiple)."""
     _case(mask_kind, score_kind, torch.bfloat16, 2, 2, 777, 777, D, 105 + D, "tcgen05")
 
 
-@pytest.mark.parametrize("fwd_variant", [1, 2])
 @pytest.mark.parametrize("Sq,Sk", [(128, 128), (100, 100), (256, 1024), (1000, 384), (129, 257), (300, 2000)])
-def test_tensor_core_shapes(Sq, Sk, fwd_variant, monkeypatch):
-    monkeypatch.setenv("FLEXATTN_FWD_VARIANT", str(fwd_variant))
+def test_tensor_core_shapes(Sq, Sk):
     _case("none", "none", torch.bfloat16, 1, 3, Sq, Sk, 128, 300 + Sq, "tcgen05")
     if Sq == Sk:
         _case("causal", "none", torch.bfloat16, 1, 3, Sq, Sk, 128, 301 + Sq, "tcgen05")
@@ -129,11 +123,10 @@ def test_tensor_core_matches_simt_on_long_rows():
 
 
 @pytest.mark.parametrize("S", [128, 256, 384])
-def test_persistent_forward_with_many_short_items(S, monkeypatch):
+def test_persistent_forward_with_many_short_items(S):
     """The persistent forward walks several work items per CTA as one kv-tile stream, with Q K^T running three tiles
     (here: up to three ITEMS) ahead of the softmax.  Many one- to three-tile items per CTA exercise every item
     boundary hazard: Q stage reuse, the first P V of an item after the previous item's epilogue, the end of the list."""
-    monkeypatch.setenv("FLEXATTN_FWD_VARIANT", "2")
     fa = _fa()
     (q, k, v, do), _ = make_qkvdo((5, 96, S, 64), (5, 96, S, 64), 600 + S, torch.bfloat16)
     sm = 0.125
@@ -145,9 +138,8 @@ def test_persistent_forward_with_many_short_items(S, monkeypatch):
     assert float((a["l"] / b["l"] - 1).abs().max()) <= 2e-2
 
 
-def test_persistent_forward_rectangular_with_many_items(monkeypatch):
+def test_persistent_forward_rectangular_with_many_items():
     """Sq != Sk, no mask, several items per CTA (every item has the same five kv tiles)."""
-    monkeypatch.setenv("FLEXATTN_FWD_VARIANT", "2")
     fa = _fa()
     (q, k, v, do), _ = make_qkvdo((4, 64, 256, 128), (4, 64, 640, 128), 611, torch.bfloat16)
     a = run_hot_path(fa, q, k, v, do, sm_scale=0.09, mask_kind="none", backend="tcgen05")
