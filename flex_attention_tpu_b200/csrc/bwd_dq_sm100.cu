@@ -1,8 +1,9 @@
-// dQ backward on the 5th-generation tensor cores (sm_100a).
+// dQ backward on the 5th-generation tensor cores (sm_100a), persistent.
 //
-// Replaces the reference's Pallas dQ kernel (flex_attention_dq_bwd.py:282-385).  One CTA owns one
-// 128-row query tile of one (batch, head): Q and dO stay in shared memory, K/V tiles stream through a
-// two-stage ring, and per kv tile
+// Replaces the reference's Pallas dQ kernel (flex_attention_dq_bwd.py:282-385).  One CTA per SM walks a list of
+// work items (128-row query tile, batch*head), in the order and dealing of the persistent forward.  Per item Q
+// and dO are copied once into tensor memory as A operands; K/V tiles stream through shared memory, and per kv
+// tile
 //
 //   S  = Q K^T, dP = dO V^T         tcgen05.mma, f32 accumulators in tensor memory (128 + 128 columns)
 //   dS = P o (dP - delta) o sigma'  in registers by two warpgroups: threads t and t + 128 own query row t and
@@ -13,25 +14,17 @@
 //                                   dQ (D columns) stays in tensor memory across kv tiles
 //
 // Because dS does not go back into the S / dP columns, those are free again as soon as the warpgroups have
-// loaded them into registers: the MMAs of tile n+1 run during the element-wise math of tile n.  The epilogue
-// scales by sm_scale and stores bf16.  Masks run only on partial tiles.
+// loaded them into registers: the MMAs of tile n+1 run during the element-wise math of tile n.
+//
+// Shared memory holds ONE ring of three 2-tile stages for everything that is loaded: the ring entries of a
+// CTA are, in order, [Q, dO of item 0], [K, V of its tile 0], [K, V of tile 1] ... [Q, dO of item 1] ... so the
+// loads of the next item are in flight while the current one is still being computed.  A stage is released by
+// the MMA issuer: with tcgen05.commit after the dQ MMA that read a K/V entry, with a plain arrive once every
+// warp has copied a Q/dO entry into tensor memory.  The epilogue (dQ * sm_scale as bf16) is staged in the dS
+// tile and leaves through TMA bulk stores.  Masks run only on partial tiles.
+#include "sched.cuh"
 #include "sm100.cuh"
 
-#ifdef FLEXATTN_TRACE
-#define FA_TRACE(slot)                                                          \
-  do {                                                                          \
-    if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64)     \
-      P.trace[n * 16 + (slot)] = clock64();                                     \
-  } while (0)
-#define FA_MARK(slot)                                                           \
-  do {                                                                          \
-    if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) \
-      P.trace[63 * 16 + (slot)] = clock64();                                    \
-  } while (0)
-#else
-#define FA_TRACE(slot)
-#define FA_MARK(slot)
-#endif
 
 namespace flexattn {
 namespace {
@@ -39,9 +32,16 @@ namespace {
 constexpr int kThreads = 320;  // warps 0-3, 4-7: element-wise warpgroups (64 key columns each); 8: MMA; 9: TMA
 constexpr int kMmaWarp = 8, kTmaWarp = 9;
 
+constexpr int kStages = 3;
+constexpr long long kDqL2Budget = 16ll << 20;  // K + V bytes live at a time (sets the head group size of the item list)
+
 struct DqSmem {
-  uint64_t bar_q, bar_qtm, bar_kv[3], bar_sdp, bar_ld, bar_ds, bar_dq;
+  uint64_t bar_full[kStages], bar_free[kStages], bar_qtm, bar_sdp, bar_ld, bar_ds, bar_dq;
   uint32_t tmem_base;
+  // descriptors of the CTA's items (ring): written by the producer, which walks the item list, and read by the
+  // MMA issuer and the warpgroups (after the Q/dO entry of the item has landed)
+  int4 item_a[8];  // {batch*head, q tile, first kv tile, end kv tile}
+  int2 item_b[8];  // {first fully kept kv tile, end of the fully kept run}
   alignas(16) int32_t doc[2][kTile];
 };
 
@@ -119,36 +119,28 @@ __global__ void __launch_bounds__(kThreads, 1)
                     const __grid_constant__ CUtensorMap tm_dq, const DevParams P, int* abort_flag) {
   constexpr int kPanels = D / 64;
   constexpr uint32_t kTileBytes = kPanels * ptx::kPanelBytes;
-  constexpr uint32_t kDsBytes = 2 * ptx::kPanelBytes;  // dS tile: 128 query rows x 128 keys, bf16
+  constexpr uint32_t kStageBytes = 2 * kTileBytes;      // [K, V] or [Q, dO]
+  constexpr uint32_t kDsBytes = 2 * ptx::kPanelBytes;   // dS tile: 128 query rows x 128 keys, bf16
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 256;
   constexpr uint32_t kColQ = 384, kColDO = 384 + D / 2;  // Q and dO as packed bf16 A operands (D/2 columns each)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  // K/V ring of three stages (stage s: K at 2s, V at 2s+1 tiles).  Stage 2 first stages Q and dO, which are
-  // copied to tensor memory once and then never read from shared memory again.
-  uint8_t* sKV = smem;
-  uint8_t* sQ = smem + 4 * kTileBytes;
-  uint8_t* sDO = smem + 5 * kTileBytes;
-  uint8_t* sDS = smem + 6 * kTileBytes;
-  DqSmem* sh = reinterpret_cast<DqSmem*>(smem + 6 * kTileBytes + kDsBytes);
+  uint8_t* sRing = smem;
+  uint8_t* sDS = smem + kStages * kStageBytes;
+  DqSmem* sh = reinterpret_cast<DqSmem*>(smem + kStages * kStageBytes + kDsBytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qt = P.n_qt - 1 - (int)blockIdx.x;
-  const int bh = blockIdx.y, b = bh / P.heads, h = bh % P.heads;
-  const int4 rm = P.row_map[(size_t)(P.map_rows > 1 ? b : 0) * P.n_qt + qt];
-  const int N = rm.y - rm.x;
 
-  FA_MARK(0);
   if (*reinterpret_cast<volatile int*>(abort_flag) != 0) return;
 
   if (tid == 0) {
-    ptx::mbar_init(&sh->bar_q, 1);
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&sh->bar_full[s], 1);
+      ptx::mbar_init(&sh->bar_free[s], 1);
+    }
     ptx::mbar_init(&sh->bar_qtm, 8);  // one arrival per warp of the two warpgroups, here and below
-    ptx::mbar_init(&sh->bar_kv[0], 1);
-    ptx::mbar_init(&sh->bar_kv[1], 1);
-    ptx::mbar_init(&sh->bar_kv[2], 1);
     ptx::mbar_init(&sh->bar_sdp, 1);
     ptx::mbar_init(&sh->bar_ld, 8);
     ptx::mbar_init(&sh->bar_ds, 8);
@@ -163,59 +155,77 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
-  FA_MARK(1);
 
+  // In every role: e = index of a ring entry in this CTA's stream (stage e % 3, barrier phase (e / 3) & 1),
+  // T = index of a kv tile in the stream (phase T & 1 of the per-tile barriers), r = index of an item.
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && N > 0) {
+    if (lane == 0) {
       bool ok = true;
       ptx::prefetch_tensormap(&tm_q);
       ptx::prefetch_tensormap(&tm_do);
       ptx::prefetch_tensormap(&tm_k);
       ptx::prefetch_tensormap(&tm_v);
-      ptx::mbar_arrive_expect_tx(&sh->bar_q, 2 * kTileBytes);
-#pragma unroll
-      for (int p = 0; p < kPanels; ++p) {
-        ptx::tma_load_3d(sQ + p * ptx::kPanelBytes, &tm_q, &sh->bar_q, p * 64, qt * kTile, bh);
-        ptx::tma_load_3d(sDO + p * ptx::kPanelBytes, &tm_do, &sh->bar_q, p * 64, qt * kTile, bh);
-      }
-      for (int n = 0; n < N && ok; ++n) {
-        const int st = n % 3;
-        if (n == 2) {  // stage 2 staged Q and dO: wait until they have been copied to tensor memory
-          ok = ptx::mbar_wait(&sh->bar_qtm, 0);
-          if (!ok) break;
-        } else if (n >= 3) {  // the stage held tile n-3, whose last reader is the dQ MMA of that tile
-          ok = ptx::mbar_wait(&sh->bar_dq, (n - 3) & 1);
-          if (!ok) break;
-        }
-        uint8_t* dK = sKV + (2 * st) * kTileBytes;
-        uint8_t* dV = sKV + (2 * st + 1) * kTileBytes;
-        ptx::mbar_arrive_expect_tx(&sh->bar_kv[st], 2 * kTileBytes);
+      int e = 0, r = 0;
+      auto acquire = [&]() -> uint8_t* {  // the stage of entry e, once the entry that used it before is done
+        const int st = e % kStages;
+        if (e >= kStages) ok = ptx::mbar_wait(&sh->bar_free[st], (uint32_t)((e / kStages - 1) & 1));
+        return sRing + st * kStageBytes;
+      };
+      for (ItemCursor it(P, kDqL2Budget); ok && it.valid(); it.next(), ++r) {
+        const int bh = it.bh(), first = it.rm.x, N = it.tiles();
+        uint8_t* dst = acquire();
+        if (!ok) break;
+        sh->item_a[r & 7] = make_int4(bh, it.qt(), it.rm.x, it.rm.y);
+        sh->item_b[r & 7] = make_int2(it.rm.z, it.rm.w);
+        uint64_t* bar = &sh->bar_full[e % kStages];
+        ptx::mbar_arrive_expect_tx(bar, kStageBytes);
 #pragma unroll
         for (int p = 0; p < kPanels; ++p) {
-          ptx::tma_load_3d(dK + p * ptx::kPanelBytes, &tm_k, &sh->bar_kv[st], p * 64, (rm.x + n) * kTile, bh);
-          ptx::tma_load_3d(dV + p * ptx::kPanelBytes, &tm_v, &sh->bar_kv[st], p * 64, (rm.x + n) * kTile, bh);
+          ptx::tma_load_3d(dst + p * ptx::kPanelBytes, &tm_q, bar, p * 64, it.qt() * kTile, bh);
+          ptx::tma_load_3d(dst + kTileBytes + p * ptx::kPanelBytes, &tm_do, bar, p * 64, it.qt() * kTile, bh);
+        }
+        ++e;
+        for (int n = 0; n < N && ok; ++n, ++e) {
+          dst = acquire();
+          if (!ok) break;
+          bar = &sh->bar_full[e % kStages];
+          ptx::mbar_arrive_expect_tx(bar, kStageBytes);
+#pragma unroll
+          for (int p = 0; p < kPanels; ++p) {
+            ptx::tma_load_3d(dst + p * ptx::kPanelBytes, &tm_k, bar, p * 64, (first + n) * kTile, bh);
+            ptx::tma_load_3d(dst + kTileBytes + p * ptx::kPanelBytes, &tm_v, bar, p * 64, (first + n) * kTile, bh);
+          }
         }
       }
       if (!ok) give_up(abort_flag, P.status, 2, 20);
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
-    // Q and dO are A operands from tensor memory (the warpgroups copy them there once): an MMA with both
-    // operands in shared memory reads 8 KB per 64 cycles, the whole shared-memory bandwidth of the SM, and this
-    // kernel also streams K, V and dS through shared memory.  S(n+1), dP(n+1) are issued as soon as the warpgroups have READ S(n), dP(n) out of tensor memory (dS goes
-    // back through shared memory, not through the S columns), so the tensor core works on the next tile while
-    // the warpgroups do the element-wise math of this one; dQ += dS(n) K(n) follows when dS(n) is in place.
-    if (lane == 0 && N > 0) {
+    // Q and dO are A operands from tensor memory: an MMA with both operands in shared memory reads 8 KB per 64
+    // cycles, the whole shared-memory bandwidth of the SM, and this kernel also streams K, V and dS through
+    // shared memory.  S(T+1), dP(T+1) are issued as soon as the warpgroups have READ S(T), dP(T) out of tensor
+    // memory, so the tensor core works on the next tile while the warpgroups do the element-wise math of this
+    // one; dQ += dS(T) K(T) follows when dS(T) is in place.  This thread does no index arithmetic: it walks the
+    // rounds of the item list and takes each item's tile count from the producer.
+    if (lane == 0) {
       bool ok = true;
       int fail_at = 1;
       constexpr uint32_t idesc_s = ptx::make_idesc(128, 128, false);
       constexpr uint32_t idesc_dq = ptx::make_idesc(128, D, true);
       const ptx::DescBase bDS = ptx::base_kmajor(ptx::smem_u32(sDS));
-      const uint32_t aKV = ptx::smem_u32(sKV);
-      auto issue_sdp = [&](int n) {
-        const uint32_t st_off = (uint32_t)(n % 3) * 2 * kTileBytes;
-        const ptx::DescBase bK = ptx::base_kmajor(aKV + st_off), bV = ptx::base_kmajor(aKV + st_off + kTileBytes);
+      const uint32_t aRing = ptx::smem_u32(sRing);
+      const int total = P.n_qt * P.batch * P.heads, G = (int)gridDim.x, c = (int)blockIdx.x;
+      // ring position of the next entry: stage e % 3 and fill phase (e / 3) & 1, kept as counters (this thread's
+      // instruction count per MMA bounds the kernel)
+      uint32_t st = 0, ph = 0;
+      int T = 0;
+      auto advance = [&]() {
+        if (++st == kStages) { st = 0; ph ^= 1u; }
+      };
+      auto issue_sdp = [&](uint32_t stage) {  // S = Q K^T, dP = dO V^T with the K/V in ring stage `stage`
+        const uint32_t st_off = stage * kStageBytes;
+        const ptx::DescBase bK = ptx::base_kmajor(aRing + st_off), bV = ptx::base_kmajor(aRing + st_off + kTileBytes);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           ptx::mma_ts(tmem + kColS, tmem + kColQ + kk * 8, ptx::desc_at(bK, ptx::koff_kmajor(kk)), idesc_s, kk > 0);
@@ -224,34 +234,63 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::mma_ts(tmem + kColDP, tmem + kColDO + kk * 8, ptx::desc_at(bV, ptx::koff_kmajor(kk)), idesc_s, kk > 0);
         ptx::mma_commit(&sh->bar_sdp);
       };
-      ok = ptx::mbar_wait(&sh->bar_qtm, 0) && ptx::mbar_wait(&sh->bar_kv[0], 0);  // Q, dO in tensor memory; K, V landed
-      if (ok) {
-        ptx::tc_fence_after();
-        issue_sdp(0);
-      }
-      for (int n = 0; n < N && ok; ++n) {
-        const uint32_t par = n & 1;
-        if (n + 1 < N) {
-          ok = ptx::mbar_wait(&sh->bar_ld, par);  // S(n), dP(n) are in registers: their columns are free
-          if (!ok) { fail_at = 2; break; }
-          FA_TRACE(0);
-          ok = ptx::mbar_wait(&sh->bar_kv[(n + 1) % 3], ((n + 1) / 3) & 1);
-          if (!ok) { fail_at = 3; break; }
+      auto item_exists = [&](int r) { return r * G + ((r & 1) ? G - 1 - c : c) < total; };
+      // Waits until Q, dO of item r are in tensor memory, releases their ring stage and issues the item's first S, dP.
+      // Returns the item's number of kv tiles.
+      auto start_item = [&](int r) -> int {
+        ok = ptx::mbar_wait(&sh->bar_qtm, r & 1);
+        if (!ok) { fail_at = 2; return 0; }
+        const int4 ia = sh->item_a[r & 7];
+        const int n_tiles = ia.w - ia.z;
+        ptx::mbar_arrive(&sh->bar_free[st]);  // the Q/dO entry has been copied out of its stage
+        advance();
+        if (n_tiles > 0) {
+          ok = ptx::mbar_wait(&sh->bar_full[st], ph);
+          if (!ok) { fail_at = 3; return 0; }
           ptx::tc_fence_after();
-          issue_sdp(n + 1);
-          FA_TRACE(1);
+          issue_sdp(st);
         }
-        ok = ptx::mbar_wait(&sh->bar_ds, par);  // dS(n) written to shared memory
-        if (!ok) { fail_at = 4; break; }
-        FA_TRACE(2);
-        ptx::tc_fence_after();
-        const ptx::DescBase bKt = ptx::base_mnmajor(aKV + (uint32_t)(n % 3) * 2 * kTileBytes);
+        return n_tiles;
+      };
+      int N = item_exists(0) ? start_item(0) : 0;
+      for (int r = 0; ok && item_exists(r); ++r) {
+        int N_next = 0;
+        bool started_next = false;
+        for (int n = 0; n < N && ok; ++n, ++T) {
+          const uint32_t par = T & 1;
+          const uint32_t cur = st;  // stage of this tile's K/V
+          advance();
+          if (n + 1 < N) {
+            ok = ptx::mbar_wait(&sh->bar_ld, par);  // S(T), dP(T) are in registers: their columns are free
+            if (!ok) { fail_at = 4; break; }
+            ok = ptx::mbar_wait(&sh->bar_full[st], ph);
+            if (!ok) { fail_at = 5; break; }
+            ptx::tc_fence_after();
+            issue_sdp(st);
+          } else if (item_exists(r + 1)) {
+            // last tile of the item: the warpgroups copy the next item's Q, dO into tensor memory before they read
+            // this tile's S, dP, so the next item's first S, dP can run during this tile's element-wise math, the dQ
+            // MMA and the epilogue
+            ok = ptx::mbar_wait(&sh->bar_ld, par);
+            if (!ok) { fail_at = 4; break; }
+            N_next = start_item(r + 1);
+            started_next = true;
+            if (!ok) break;
+          }
+          ok = ptx::mbar_wait(&sh->bar_ds, par);  // dS(T) written to shared memory
+          if (!ok) { fail_at = 6; break; }
+          ptx::tc_fence_after();
+          const ptx::DescBase bKt = ptx::base_mnmajor(aRing + cur * kStageBytes);
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          ptx::mma_ss(tmem + kColDQ, ptx::desc_at(bDS, ptx::koff_kmajor(kk)), ptx::desc_at(bKt, ptx::koff_mnmajor(kk)),
-                      idesc_dq, (n > 0) || (kk > 0));
-        ptx::mma_commit(&sh->bar_dq);
-        FA_TRACE(3);
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            ptx::mma_ss(tmem + kColDQ, ptx::desc_at(bDS, ptx::koff_kmajor(kk)), ptx::desc_at(bKt, ptx::koff_mnmajor(kk)),
+                        idesc_dq, (n > 0) || (kk > 0));
+          ptx::mma_commit(&sh->bar_dq);
+          ptx::mma_commit(&sh->bar_free[cur]);  // K/V of this entry have been read
+        }
+        if (!ok) break;
+        if (!started_next && item_exists(r + 1)) N_next = start_item(r + 1);  // (items without kv tiles)
+        N = N_next;
       }
       if (!ok) give_up(abort_flag, P.status, 2, fail_at);
     }
@@ -259,171 +298,206 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ------------------------------------------------------------------ element-wise warpgroups
     const int row = tid & 127;   // query row inside the tile = TMEM lane
     const int half = tid >> 7;   // which 64 key columns of every tile this thread handles
-    const int i = qt * kTile + row;
-    const bool row_ok = i < P.seq_q;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float c2 = P.sm_scale * kLog2e;
-    const float slope2 = (SK == FLEXATTN_SCORE_ALIBI) ? P.alibi_slopes[h] * kLog2e : 0.f;
     const float capl2 = P.cap * kLog2e;
     const float csc = (SK == FLEXATTN_SCORE_SOFTCAP) ? P.sm_scale / P.cap : 0.f;
-    const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
-    const int di = (MK == FLEXATTN_MASK_DOCUMENT && row_ok) ? doc[i] : 0;
-    const size_t grow = (size_t)bh * P.seq_q + i;
-    float nlse2 = ptx::kRoundLog2, delta = 0.f;
-    if (row_ok) {
-      const float l = P.l[grow];
-      // l == 0 (fully masked row): force p to 0; kRoundLog2 pre-scales p (and so dS) for pack_bf16_trunc
-      nlse2 = l > 0.f ? ptx::kRoundLog2 - fmaf(P.m[grow], kLog2e, log2f(l)) : -1.0e30f;
-      delta = P.delta[grow];
-    }
     // this thread's 128 bytes of the dS tile: row `row` of panel `half`, 16-byte chunk j at slot j ^ (row & 7)
     uint8_t* ds_row = sDS + half * ptx::kPanelBytes + row * 128;
     bool ok = true;
     int fail_at = 0;
+    int e = 0, T = 0;
+    const int total = P.n_qt * P.batch * P.heads, G = (int)gridDim.x, cta = (int)blockIdx.x;
+    // row statistics of the NEXT item, fetched early when its descriptor is already there
+    bool pf_have = false;
+    float pf_l = 0.f, pf_m = 0.f, pf_delta = 0.f;
+    int pf_di = 0;
+    auto row_stats = [&](const int4 ia, float& l, float& m, float& dl, int& di_out) {
+      const int i = ia.y * kTile + row;
+      l = 0.f; m = 0.f; dl = 0.f; di_out = 0;
+      if (i < P.seq_q) {
+        const size_t g = (size_t)ia.x * P.seq_q + i;
+        l = P.l[g];
+        m = P.m[g];
+        dl = P.delta[g];
+        if (MK == FLEXATTN_MASK_DOCUMENT) di_out = (P.doc_ids + (size_t)(ia.x / P.heads) * P.doc_stride)[i];
+      }
+    };
 
-    // Q and dO rows -> tensor memory as packed bf16 (element d of row r at lane r, column d / 2).  Thread (row,
-    // half) moves the 64 elements of 128-byte panel `half`: chunk j of the row sits at slot j ^ (row & 7).
-    if (N > 0) {
-      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_q, 0));
-      FA_MARK(2);
-      if (!ok) fail_at = 9;
-      if (ok) {
-        if constexpr (D == 128) {
+    // Q and dO rows of an item -> tensor memory as packed bf16 (element d of row r at lane r, column d / 2), from ring
+    // entry `entry`.  Thread (row, half) moves the 64 elements of 128-byte panel `half`: chunk j of the row sits at
+    // slot j ^ (row & 7).  Every MMA that read the previous Q / dO must have completed: the caller has waited for
+    // the S / dP of the previous item's last tile.
+    auto copy_q_do = [&](int entry) {
+      const uint8_t* sQ = sRing + (entry % kStages) * kStageBytes;
+      const uint8_t* sDO = sQ + kTileBytes;
+      if constexpr (D == 128) {
 #pragma unroll
-          for (int which = 0; which < 2; ++which) {
-            const uint8_t* src = (which ? sDO : sQ) + half * ptx::kPanelBytes + row * 128;
-            uint32_t r[32];
-#pragma unroll
-            for (int jc = 0; jc < 8; ++jc) {
-              const uint4 v4 = *reinterpret_cast<const uint4*>(src + ((jc ^ (row & 7)) << 4));
-              r[4 * jc] = v4.x; r[4 * jc + 1] = v4.y; r[4 * jc + 2] = v4.z; r[4 * jc + 3] = v4.w;
-            }
-            ptx::tmem_st32(lane_base + (which ? kColDO : kColQ) + half * 32, r);
-          }
-        } else {  // D == 64: one panel per tensor; warpgroup 0 moves Q, warpgroup 1 moves dO
-          const uint8_t* src = (half ? sDO : sQ) + row * 128;
-          uint32_t r[32];
+        for (int which = 0; which < 2; ++which) {
+          const uint8_t* src = (which ? sDO : sQ) + half * ptx::kPanelBytes + row * 128;
+          uint32_t rr[32];
 #pragma unroll
           for (int jc = 0; jc < 8; ++jc) {
             const uint4 v4 = *reinterpret_cast<const uint4*>(src + ((jc ^ (row & 7)) << 4));
-            r[4 * jc] = v4.x; r[4 * jc + 1] = v4.y; r[4 * jc + 2] = v4.z; r[4 * jc + 3] = v4.w;
+            rr[4 * jc] = v4.x; rr[4 * jc + 1] = v4.y; rr[4 * jc + 2] = v4.z; rr[4 * jc + 3] = v4.w;
           }
-          ptx::tmem_st32(lane_base + (half ? kColDO : kColQ), r);
+          ptx::tmem_st32(lane_base + (which ? kColDO : kColQ) + half * 32, rr);
         }
-        ptx::tmem_wait_st();
-        ptx::tc_fence_before();
-      }
-      ptx::mbar_arrive_warp(&sh->bar_qtm);
-      FA_MARK(3);
-    }
-
-    for (int n = 0; n < N; ++n) {
-      const int kt = rm.x + n, j0 = kt * kTile + 64 * half;  // first key position of this thread's columns
-      const bool partial = !(kt >= rm.z && kt < rm.w);
-      if (MK == FLEXATTN_MASK_DOCUMENT && partial) {
-        if (row < 64) {
-          const int j = j0 + row;
-          sh->doc[n & 1][64 * half + row] = (j < P.seq_k) ? doc[j] : -1;
+      } else {  // D == 64: one panel per tensor; warpgroup 0 moves Q, warpgroup 1 moves dO
+        const uint8_t* src = (half ? sDO : sQ) + row * 128;
+        uint32_t rr[32];
+#pragma unroll
+        for (int jc = 0; jc < 8; ++jc) {
+          const uint4 v4 = *reinterpret_cast<const uint4*>(src + ((jc ^ (row & 7)) << 4));
+          rr[4 * jc] = v4.x; rr[4 * jc + 1] = v4.y; rr[4 * jc + 2] = v4.z; rr[4 * jc + 3] = v4.w;
         }
-        ptx::named_bar_sync(1 + half, 128);
+        ptx::tmem_st32(lane_base + (half ? kColDO : kColQ), rr);
       }
-      // a failed wait never leaves the loop early: every thread keeps executing the same named barriers
-      if (ok) {
-        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_sdp, n & 1));
-        if (!ok) fail_at = 10;
-      }
-      if (!ok) continue;
-      if (tid == 0) FA_TRACE(8);
-      if (n == 0) FA_MARK(4);
-      ptx::tc_fence_after();
-      uint32_t sr[2][32], pr[2][32];
-      ptx::tmem_ld32(lane_base + kColS + half * 64, sr[0]);
-      ptx::tmem_ld32(lane_base + kColS + half * 64 + 32, sr[1]);
-      ptx::tmem_ld32(lane_base + kColDP + half * 64, pr[0]);
-      ptx::tmem_ld32(lane_base + kColDP + half * 64 + 32, pr[1]);
-      ptx::tmem_wait_ld();
-      ptx::tmem_ld_acquire(sr[0]);
-      ptx::tmem_ld_acquire(sr[1]);
-      ptx::tmem_ld_acquire(pr[0]);
-      ptx::tmem_ld_acquire(pr[1]);
+      ptx::tmem_wait_st();
       ptx::tc_fence_before();
-      ptx::mbar_arrive_warp(&sh->bar_ld);  // S / dP columns may be overwritten by the next tile's MMAs
-      if (tid == 0) FA_TRACE(9);
-      uint32_t pk[32];
-      const float abase = slope2 * (float)(j0 - i);
-      if (partial)
-        dq_half_math<SK, MK, true>(sr, pr, pk, nlse2, delta, &sh->doc[n & 1][64 * half], i, di, j0, P.seq_k, P.window,
-                                   P.stride, c2, slope2, abase, capl2, csc);
-      else
-        dq_half_math<SK, MK, false>(sr, pr, pk, nlse2, delta, &sh->doc[n & 1][64 * half], i, di, j0, P.seq_k, P.window,
-                                    P.stride, c2, slope2, abase, capl2, csc);
-      if (tid == 0) FA_TRACE(10);
-      if (n > 0) {  // the dQ MMA of the previous tile must have read the dS buffer
-        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dq, (n - 1) & 1));
-        if (!ok) { fail_at = 11; continue; }
-      }
-#pragma unroll
-      for (int jc = 0; jc < 8; ++jc) {
-        const uint4 v4 = make_uint4(pk[4 * jc], pk[4 * jc + 1], pk[4 * jc + 2], pk[4 * jc + 3]);
-        *reinterpret_cast<uint4*>(ds_row + ((jc ^ (row & 7)) << 4)) = v4;
-      }
-      ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the MMA's shared-memory reads
-      ptx::mbar_arrive_warp(&sh->bar_ds);
-      if (tid == 0) FA_TRACE(11);
-    }
+      ptx::mbar_arrive_warp(&sh->bar_qtm);
+    };
+    bool copied_ahead = false;  // this item's Q, dO were already copied during the previous item's last tile
 
-    FA_MARK(5);
-    if (ok && N > 0) {
-      ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dq, (N - 1) & 1));
-      if (!ok) fail_at = 12;
-    }
-    FA_MARK(6);
-    // Epilogue: dQ * sm_scale as bf16 into a shared-memory tile in the TMA (128-byte swizzle) layout, then one
-    // bulk tensor store per 64-column panel.  The K/V ring is free by now (every MMA has completed); rows past
-    // seq_q are clipped by the tensor map.
-    if (ok) {
-      if (N > 0) ptx::tc_fence_after();
-      const float sc = P.sm_scale;
-      uint8_t* stage_row = sKV + row * 128;
-#pragma unroll 1
-      for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
-        uint32_t r[32];
-        if (N > 0) {
-          ptx::tmem_ld32(lane_base + kColDQ + c0, r);
-          ptx::tmem_wait_ld();
-          ptx::tmem_ld_acquire(r);
-        } else {
-#pragma unroll
-          for (int c = 0; c < 32; ++c) r[c] = 0u;
-        }
-#pragma unroll
-        for (int c = 0; c < 32; c += 8) {
-          uint4 v4;
-          v4.x = ptx::pack_bf16(__uint_as_float(r[c]) * sc, __uint_as_float(r[c + 1]) * sc);
-          v4.y = ptx::pack_bf16(__uint_as_float(r[c + 2]) * sc, __uint_as_float(r[c + 3]) * sc);
-          v4.z = ptx::pack_bf16(__uint_as_float(r[c + 4]) * sc, __uint_as_float(r[c + 5]) * sc);
-          v4.w = ptx::pack_bf16(__uint_as_float(r[c + 6]) * sc, __uint_as_float(r[c + 7]) * sc);
-          const int col = c0 + c, panel = col >> 6, chunk = (col & 63) >> 3;
-          *reinterpret_cast<uint4*>(stage_row + panel * ptx::kPanelBytes + ((chunk ^ (row & 7)) << 4)) = v4;
-        }
+    for (int r = 0; r * G + ((r & 1) ? G - 1 - cta : cta) < total; ++r) {
+      // the Q/dO entry of the item has landed, and with it the item's descriptor
+      if (ok && !copied_ahead) {
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_full[e % kStages], (uint32_t)((e / kStages) & 1)));
+        if (!ok) fail_at = 9;
       }
-      ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the bulk store
-    }
-    ptx::named_bar_sync(3, 256);
-    if (ok && tid == 0) {
+      const int4 ia = sh->item_a[r & 7];
+      const int2 ib = sh->item_b[r & 7];
+      const int bh = ia.x, qt = ia.y, b = bh / P.heads, h = bh % P.heads;
+      const int4 rm = make_int4(ia.z, ia.w, ib.x, ib.y);
+      const int N = rm.y - rm.x;
+      const int i = qt * kTile + row;
+      const bool row_ok = i < P.seq_q;
+      const float slope2 = (SK == FLEXATTN_SCORE_ALIBI) ? P.alibi_slopes[h] * kLog2e : 0.f;
+      const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
+      float l_, m_, delta;
+      int di;
+      if (pf_have) { l_ = pf_l; m_ = pf_m; delta = pf_delta; di = pf_di; }
+      else row_stats(ia, l_, m_, delta, di);
+      pf_have = false;
+      // l == 0 (fully masked row): force p to 0; kRoundLog2 pre-scales p (and so dS) for pack_bf16_trunc
+      const float nlse2 = row_ok ? (l_ > 0.f ? ptx::kRoundLog2 - fmaf(m_, kLog2e, log2f(l_)) : -1.0e30f) : ptx::kRoundLog2;
+
+      if (ok && !copied_ahead) copy_q_do(e);
+      copied_ahead = false;
+      ++e;
+      const bool has_next = (r + 1) * G + (((r + 1) & 1) ? G - 1 - cta : cta) < total;
+
+      for (int n = 0; n < N; ++n, ++T, ++e) {
+        const int kt = rm.x + n, j0 = kt * kTile + 64 * half;  // first key position of this thread's columns
+        const bool partial = !(kt >= rm.z && kt < rm.w);
+        if (MK == FLEXATTN_MASK_DOCUMENT && partial) {
+          if (row < 64) {
+            const int j = j0 + row;
+            sh->doc[T & 1][64 * half + row] = (j < P.seq_k) ? doc[j] : -1;
+          }
+          ptx::named_bar_sync(1 + half, 128);
+        }
+        // a failed wait never leaves the loops early: every thread keeps executing the same named barriers
+        if (ok) {
+          ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_sdp, T & 1));
+          if (!ok) fail_at = 10;
+        }
+        if (!ok) continue;
+        ptx::tc_fence_after();
+        if (n == N - 1 && has_next) {
+          // Last tile of the item: every MMA that reads this item's Q, dO has completed (S, dP of this tile are
+          // ready), so the next item's Q, dO go into tensor memory now.  Its first S, dP then run during this
+          // tile's element-wise math, the last dQ MMA and the epilogue.  Entry e + 1 of the ring is that Q/dO pair.
+          ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_full[(e + 1) % kStages], (uint32_t)(((e + 1) / kStages) & 1)));
+          if (!ok) { fail_at = 13; continue; }
+          copy_q_do(e + 1);
+          copied_ahead = true;
+          row_stats(sh->item_a[(r + 1) & 7], pf_l, pf_m, pf_delta, pf_di);  // and its row statistics are fetched early
+          pf_have = true;
+        }
+        uint32_t sr[2][32], pr[2][32];
+        ptx::tmem_ld32(lane_base + kColS + half * 64, sr[0]);
+        ptx::tmem_ld32(lane_base + kColS + half * 64 + 32, sr[1]);
+        ptx::tmem_ld32(lane_base + kColDP + half * 64, pr[0]);
+        ptx::tmem_ld32(lane_base + kColDP + half * 64 + 32, pr[1]);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld_acquire(sr[0]);
+        ptx::tmem_ld_acquire(sr[1]);
+        ptx::tmem_ld_acquire(pr[0]);
+        ptx::tmem_ld_acquire(pr[1]);
+        ptx::tc_fence_before();
+        ptx::mbar_arrive_warp(&sh->bar_ld);  // S / dP columns may be overwritten by the next tile's MMAs
+        uint32_t pk[32];
+        const float abase = slope2 * (float)(j0 - i);
+        if (partial)
+          dq_half_math<SK, MK, true>(sr, pr, pk, nlse2, delta, &sh->doc[T & 1][64 * half], i, di, j0, P.seq_k, P.window,
+                                     P.stride, c2, slope2, abase, capl2, csc);
+        else
+          dq_half_math<SK, MK, false>(sr, pr, pk, nlse2, delta, &sh->doc[T & 1][64 * half], i, di, j0, P.seq_k, P.window,
+                                      P.stride, c2, slope2, abase, capl2, csc);
+        if (n > 0) {  // the dQ MMA of the previous tile must have read the dS buffer
+          ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dq, (T - 1) & 1));
+          if (!ok) { fail_at = 11; continue; }
+        }
 #pragma unroll
-      for (int p = 0; p < kPanels; ++p) ptx::tma_store_3d(&tm_dq, sKV + p * ptx::kPanelBytes, p * 64, qt * kTile, bh);
-      ptx::tma_store_commit();
-      ptx::tma_store_wait_read();  // shared memory must stay intact until the store has read it
+        for (int jc = 0; jc < 8; ++jc) {
+          const uint4 v4 = make_uint4(pk[4 * jc], pk[4 * jc + 1], pk[4 * jc + 2], pk[4 * jc + 3]);
+          *reinterpret_cast<uint4*>(ds_row + ((jc ^ (row & 7)) << 4)) = v4;
+        }
+        ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the MMA's shared-memory reads
+        ptx::mbar_arrive_warp(&sh->bar_ds);
+      }
+
+      // ---- item epilogue: dQ * sm_scale as bf16 into the dS tile (free: the last dQ MMA has read it) in the TMA
+      // (128-byte swizzle) layout, then one bulk tensor store per 64-column panel; rows past seq_q are clipped
+      // by the tensor map.
+      if (ok && N > 0) {
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dq, (T - 1) & 1));
+        if (!ok) fail_at = 12;
+      }
+      if (ok) {
+        if (N > 0) ptx::tc_fence_after();
+        const float sc = P.sm_scale;
+        uint8_t* stage_row = sDS + row * 128;
+#pragma unroll 1
+        for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
+          uint32_t rr[32];
+          if (N > 0) {
+            ptx::tmem_ld32(lane_base + kColDQ + c0, rr);
+            ptx::tmem_wait_ld();
+            ptx::tmem_ld_acquire(rr);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) rr[c] = 0u;
+          }
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint4 v4;
+            v4.x = ptx::pack_bf16(__uint_as_float(rr[c]) * sc, __uint_as_float(rr[c + 1]) * sc);
+            v4.y = ptx::pack_bf16(__uint_as_float(rr[c + 2]) * sc, __uint_as_float(rr[c + 3]) * sc);
+            v4.z = ptx::pack_bf16(__uint_as_float(rr[c + 4]) * sc, __uint_as_float(rr[c + 5]) * sc);
+            v4.w = ptx::pack_bf16(__uint_as_float(rr[c + 6]) * sc, __uint_as_float(rr[c + 7]) * sc);
+            const int col = c0 + c, panel = col >> 6, chunk = (col & 63) >> 3;
+            *reinterpret_cast<uint4*>(stage_row + panel * ptx::kPanelBytes + ((chunk ^ (row & 7)) << 4)) = v4;
+          }
+        }
+        if (N > 0) ptx::tc_fence_before();
+        ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the bulk store
+      }
+      ptx::named_bar_sync(3, 256);
+      if (ok && tid == 0) {
+#pragma unroll
+        for (int p = 0; p < kPanels; ++p) ptx::tma_store_3d(&tm_dq, sDS + p * ptx::kPanelBytes, p * 64, qt * kTile, bh);
+        ptx::tma_store_commit();
+        ptx::tma_store_wait_read();  // the dS tile is written again by the next item's first tile
+      }
+      ptx::named_bar_sync(3, 256);
     }
     if (!ok && lane == 0) give_up(abort_flag, P.status, 2, fail_at);
-
-    FA_MARK(7);
   }
 
   ptx::tc_fence_before();
   __syncthreads();
-  FA_MARK(8);
   if (warp == kMmaWarp) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, kTmemCols);
@@ -443,7 +517,11 @@ int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const
       return FLEXATTN_ERR_CUDA;
     attr_set = true;
   }
-  dim3 grid(d.n_qt, d.batch * d.heads);
+  // persistent: one CTA per SM (fewer when there are fewer work items)
+  const long long items = (long long)d.n_qt * d.batch * d.heads;
+  const int sms = sm_count();
+  if (sms <= 0) return FLEXATTN_ERR_CUDA;
+  dim3 grid((unsigned)(items < sms ? items : sms));
   kern<<<grid, kThreads, smem_req, st>>>(tq, tdo, tk, tv, tdq, d, abort_flag);
   return cudaGetLastError() == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;
 }

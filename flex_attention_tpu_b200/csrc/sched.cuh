@@ -33,12 +33,13 @@ struct ItemCursor {
     qt = __ldg(&P.order[row + rank]);
     return __ldg(&P.order_rm[row + rank]);  // the row-map entry of that q tile: two independent loads
   }
-  __device__ __forceinline__ ItemCursor(const DevParams& p) : P(p) {
+  // l2_budget: bytes of K + V that may be live at a time (sets how many heads form a group)
+  __device__ __forceinline__ explicit ItemCursor(const DevParams& p, long long l2_budget = 48ll << 20) : P(p) {
     per_row = p.heads * p.n_qt;
     total = p.batch * per_row;
-    // K + V of one slice: 2 * seq_k * head_dim * 2 bytes; keep about 48 MB of them live
+    // K + V of one slice: 2 * seq_k * head_dim * 2 bytes
     const long long slice_bytes = 4ll * p.seq_k * p.head_dim;
-    group = (int)max(1ll, min((long long)p.heads, (48ll << 20) / slice_bytes));
+    group = (int)max(1ll, min((long long)p.heads, l2_budget / slice_bytes));
     full_groups = p.heads / group;
     round = 0;
     w = item_of(0);
