@@ -44,7 +44,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel on the c2 workload, from
 # the ncu capture summarised under profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES = {"c2": {"fwd": 259.9e6, "dq": 324.6e6, "dkv": 379.7e6}}
+NCU_TRAFFIC_BYTES = {"c2": {"fwd": 276.4e6, "dq": 369.1e6, "dkv": 380.4e6}}
 
 
 def measured_peaks():
