@@ -147,3 +147,12 @@ def test_persistent_forward_rectangular_with_many_items():
     for n in ("o", "dq", "dk", "dv"):
         e = errors(a[n], b[n].float().cpu().numpy(), 2 * TOL[torch.bfloat16]["round"])   # both sides stored in bf16
         assert e["max_abs_excess"] <= TOL[torch.bfloat16]["abs"] and e["max_rel"] <= TOL[torch.bfloat16]["rel"], (n, e)
+
+
+@pytest.mark.parametrize("mask_kind,score_kind", [("document", "softcap"), ("sliding_window_causal", "alibi"),
+                                                   ("s2", "none"), ("sliding_window", "none")])
+def test_persistent_kernels_every_mask_with_many_items(mask_kind, score_kind):
+    """Several work items per CTA (the persistent forward and dQ kernels walk them as one stream) under every mask
+    family: item lengths differ from item to item, partial tiles sit at different places, document ids change with
+    the batch row."""
+    _case(mask_kind, score_kind, torch.bfloat16, 4, 48, 500, 500, 128, 900 + len(mask_kind), "tcgen05")
