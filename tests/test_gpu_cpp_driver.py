@@ -10,6 +10,8 @@ EXE = os.path.join(os.path.dirname(__file__), "..", "flex_attention_tpu_b200", "
 
 
 def test_driver_is_built():
+    if not os.path.exists(EXE):  # a fresh checkout: build the library and the driver in-tree first
+        subprocess.run(["python", os.path.join(os.path.dirname(EXE), "build.py")], check=True, timeout=1800)
     assert os.path.exists(EXE) and os.access(EXE, os.X_OK), "run python flex_attention_tpu_b200/build.py"
 
 
