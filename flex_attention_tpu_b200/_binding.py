@@ -277,16 +277,20 @@ class Problem:
         check(lib.flexattn_bwd_dkv(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_dkv")
         return dk, dv
 
-    def backward(self, q, k, v, o, do, l, m, need_dq=True, need_dkv=True, want_dab=False):
+    def backward(self, q, k, v, o, do, l, m, need_dq=True, need_dkv=True, want_dab=False, two_streams=None):
         """delta, then dQ and dK/dV.  The two gradient kernels only share inputs, so dK/dV is launched on a side
         stream: both kernels fill every SM on their own, but the tail of one then overlaps the head of the other.
-        Everything is ordered after the current stream's work and the current stream waits for both."""
+        Everything is ordered after the current stream's work and the current stream waits for both.
+        ``two_streams=False`` launches both on the current stream (the host-buffer pipeline does: there the
+        extra stream only adds synchronisation between the copy and compute streams)."""
         delta = self.preprocess(o, do)
         if want_dab:  # the bias gradient comes out of the dQ kernel
             dq, dab = self.bwd_dq(q, k, v, do, l, m, delta, want_dab=True)
             dk, dv = self.bwd_dkv(q, k, v, do, l, m, delta) if need_dkv else (None, None)
             return delta, dq, dk, dv, dab
-        if not (need_dq and need_dkv and TWO_STREAM_BACKWARD):
+        if two_streams is None:
+            two_streams = TWO_STREAM_BACKWARD
+        if not (need_dq and need_dkv and two_streams):
             dq = self.bwd_dq(q, k, v, do, l, m, delta) if need_dq else None
             dk, dv = self.bwd_dkv(q, k, v, do, l, m, delta) if need_dkv else (None, None)
             return delta, dq, dk, dv
@@ -303,7 +307,7 @@ class Problem:
 
 _SIDE_STREAMS = {}
 # dK/dV on a side stream next to dQ (see Problem.backward); False launches the two kernels one after the other
-TWO_STREAM_BACKWARD = True
+TWO_STREAM_BACKWARD = os.environ.get("FLEXATTN_TWO_STREAM", "1") != "0"
 
 
 def _side_stream(device):

@@ -36,15 +36,16 @@ class _FlexAttentionFn(torch.autograd.Function):
 
 
 def flex_attention_bwd(q, k, v, o, l, m, do, *, ab=None, segment_ids=None, causal: bool = False,
-                       sm_scale: float = 1.0, mask_fns=None, score_fn=None, backend: str = "auto"):
+                       sm_scale: float = 1.0, mask_fns=None, score_fn=None, backend: str = "auto", two_streams=None):
     """The whole backward in one call: delta = rowsum(o * do), then dQ and dK/dV (launched on two streams so
     that the tail of one kernel overlaps the head of the other).  Residuals ``o, l, m`` as returned by
     ``_flex_attention_impl(..., save_residuals=True)``; the counterpart of the reference's
-    ``_flash_attention_bwd`` (``jax_exp.py:276-321``).  Returns ``(dq, dk, dv)``."""
+    ``_flash_attention_bwd`` (``jax_exp.py:276-321``).  ``two_streams=False`` keeps both kernels on the current
+    stream.  Returns ``(dq, dk, dv)``."""
     mask_fn, block_mask_fn = mask_fns if mask_fns is not None else (None, None)
     prob = make_problem(q, k, ab=ab, segment_ids=segment_ids, causal=causal, sm_scale=sm_scale, mask_fn=mask_fn,
                         block_mask_fn=block_mask_fn, score_fn=score_fn, backend=backend)
-    _, dq, dk, dv = prob.backward(q, k, v, o, do.contiguous(), l, m)
+    _, dq, dk, dv = prob.backward(q, k, v, o, do.contiguous(), l, m, two_streams=two_streams)
     return dq, dk, dv
 
 

@@ -72,7 +72,7 @@ def fwd_bwd_from_host(q, k, v, do, *, sm_scale, mask_fn=None, block_mask_fn=None
                                            block_mask_fn, mask_fn, score_fn, backend=backend)
             dq, dk, dv = flex_attention_bwd(qd, kd, vd, o, l, m, dod, segment_ids=seg, causal=causal, sm_scale=sm_scale,
                                             mask_fns=None if mask_fn is None else (mask_fn, block_mask_fn),
-                                            score_fn=score_fn, backend=backend)
+                                            score_fn=score_fn, backend=backend, two_streams=False)
             delta = None
             ev_comp = torch.cuda.Event()
             ev_comp.record(s_comp)
