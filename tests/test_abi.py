@@ -29,9 +29,10 @@ def test_every_declared_symbol_is_exported(B):
 
 
 def test_struct_layout_matches_header(B):
-    # 13 pointers, 5+1 ints, float, int, float, 3 ints, pointer, size_t, pointer, 2 ints
+    # 13 pointers, 5+1 ints, float, int, float, 3 ints, pointer, size_t, pointer, 2 ints, then (ABI 2) ab and dab
     assert ctypes.sizeof(B.FlexAttnParams) == 200
     assert B.FlexAttnParams.workspace.offset == 152 and B.FlexAttnParams.status.offset == 168
+    assert B.FlexAttnParams.ab.offset == 184 and B.FlexAttnParams.dab.offset == 192
 
 
 def test_status_strings(B):
