@@ -2,7 +2,7 @@
 mask map) as hand-written sm_100a CUDA behind a C ABI, with the reference project's Python entry points
 (``_flex_attention_impl``, ``flex_attention_bwd_dq``, ``flash_attention_bwd_dkv`` and the ``masks`` /
 ``scores`` factories) on top.  Importing the package loads ``libflexattn.so`` and fails if it is missing."""
-from . import _binding, masks, scores, util, constants, workloads, sharding  # noqa: F401
+from . import _binding, masks, scores, util, constants, sharding  # noqa: F401
 from .flex_attention_kernel import _flex_attention_impl  # noqa: F401
 from .flex_attention_dq_bwd import flex_attention_bwd_dq, bwd_preprocess  # noqa: F401
 from .flex_attention_dkv_kernel import flash_attention_bwd_dkv  # noqa: F401

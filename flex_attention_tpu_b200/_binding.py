@@ -11,16 +11,14 @@ from collections import OrderedDict
 
 import torch
 
-# FLEXATTN_LIBRARY points at an alternative build of the same library (e.g. an instrumented one)
-_LIB_PATH = os.environ.get("FLEXATTN_LIBRARY") or os.path.join(os.path.dirname(os.path.abspath(__file__)),
-                                                               "libflexattn.so")
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libflexattn.so")
 
 DTYPE_BF16, DTYPE_F32 = 0, 1
 SCORE_NONE, SCORE_ALIBI, SCORE_SOFTCAP = 0, 1, 2
 MASK_NONE, MASK_CAUSAL, MASK_SLIDING_WINDOW, MASK_SLIDING_WINDOW_CAUSAL, MASK_DOCUMENT, MASK_S2 = range(6)
 BACKEND_AUTO, BACKEND_SIMT, BACKEND_TCGEN05 = 0, 1, 2
 TILE = 128
-ABI_VERSION = 2   # FLEXATTN_ABI_VERSION of include/flexattn.h this binding was written against
+ABI_VERSION = 3   # FLEXATTN_ABI_VERSION of include/flexattn.h this binding was written against
 
 MASK_KIND_IDS = {"none": MASK_NONE, "causal": MASK_CAUSAL, "sliding_window": MASK_SLIDING_WINDOW,
                  "sliding_window_causal": MASK_SLIDING_WINDOW_CAUSAL, "document": MASK_DOCUMENT, "s2": MASK_S2}
@@ -76,8 +74,11 @@ def _load():
                                            ctypes.POINTER(ctypes.c_int32)]
     lib.flexattn_selftest_umma.restype = ctypes.c_int
     lib.flexattn_selftest_umma.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
-                                           ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p,
-                                           ctypes.POINTER(ctypes.c_int32)]
+                                           ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
+    lib.flexattn_selftest_timeout.restype = ctypes.c_int
+    lib.flexattn_selftest_timeout.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
+    lib.flexattn_reset_abort.restype = ctypes.c_int
+    lib.flexattn_reset_abort.argtypes = [ctypes.c_void_p]
     if lib.flexattn_abi_version() != ABI_VERSION:
         raise ImportError("libflexattn.so ABI version mismatch: rebuild the library")
     return lib
@@ -101,6 +102,48 @@ def _stream_ptr(device):
 
 def _ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+# ------------------------------------------------------------------------------------------ failure mailbox
+# A device-side wait that gives up reports through four status words.  When the caller passes no `status`
+# tensor the binding supplies one of its own per device, in pinned host memory the device writes through the
+# bus: the host can then look at it at the start of every call WITHOUT synchronising, and raises on the first
+# call after the failure became visible.  A time-out is sticky on its device until `reset_abort` has run.
+_MAILBOX = {}
+
+
+def _mailbox(device):
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    box = _MAILBOX.get(key)
+    if box is None:
+        box = _MAILBOX[key] = torch.zeros(4, dtype=torch.int32).pin_memory()
+    return box
+
+
+def raise_if_failed(device):
+    """Raises FlexAttnError if an earlier launch on `device` reported a device-side time-out into the binding's
+    own status words.  Never synchronises."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    box = _MAILBOX.get(key)
+    if box is not None and int(box[0]) != 0:
+        code, kernel, block, detail = (int(x) for x in box.tolist())
+        raise FlexAttnError(code, f"an earlier launch on cuda:{key} (kernel id {kernel}, block {block}, detail {detail}; "
+                                  "outputs of launches since then are not valid; call reset_abort() to re-arm)")
+
+
+def reset_abort(device=None):
+    """Clears the device's abort word (stream-ordered on the current stream) and the binding's status words."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    check(lib.flexattn_reset_abort(_stream_ptr(device)), "flexattn_reset_abort")
+    torch.cuda.current_stream(device).synchronize()
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key in _MAILBOX:
+        _MAILBOX[key].zero_()
+
+
+# Debug switch for the test-suite: every output tensor the binding allocates is filled with NaN before the
+# kernels run, so an element a kernel failed to write cannot pass for a result left over from an earlier call.
+POISON_OUTPUTS = os.environ.get("FLEXATTN_POISON_OUTPUTS", "0") not in ("", "0")
 
 
 class Problem:
@@ -130,7 +173,7 @@ class Problem:
         p.score_kind, p.softcap = int(score_kind), float(softcap)
         p.mask_kind, p.window, p.stride = int(mask_kind), int(window), int(stride)
         p.backend = int(backend)
-        self._keep = []  # tensors whose pointers sit in `p`
+        self._keep = {}  # tensors whose pointers sit in `p`, by field name
         if mask_kind == MASK_DOCUMENT:
             if doc_ids is None:
                 raise ValueError("document mask needs segment/doc ids")
@@ -141,15 +184,17 @@ class Problem:
             if doc_ids.shape != (B, max(Sq, k.shape[2])):
                 raise ValueError(f"doc ids must be [batch, {max(Sq, k.shape[2])}], got {tuple(doc_ids.shape)}")
             p.doc_ids = doc_ids.data_ptr()
-            self._keep.append(doc_ids)
+            self._keep["doc_ids"] = doc_ids
         self.doc_ids = doc_ids if mask_kind == MASK_DOCUMENT else None
         if score_kind == SCORE_ALIBI:
             slopes = self._device_slopes(alibi_slopes, H)
             p.alibi_slopes = slopes.data_ptr()
-            self._keep.append(slopes)
-        if status is not None:
-            p.status = status.data_ptr()
-            self._keep.append(status)
+            self._keep["alibi_slopes"] = slopes
+        if status is None:
+            raise_if_failed(self.device)
+            status = _mailbox(self.device)
+        p.status = status.data_ptr()
+        self._keep["status"] = status
         self.ab = None
         if ab is not None:
             # dense additive bias [B,H,Sq,Sk], float32 (SIMT backend; the library refuses it on tcgen05)
@@ -159,7 +204,7 @@ class Problem:
                 raise ValueError(f"Attention bias shape mismatch: expected {(B, H, Sq, k.shape[2])}, got {tuple(ab.shape)}")
             self.ab = ab.to(torch.float32).contiguous()
             p.ab = self.ab.data_ptr()
-            self._keep.append(self.ab)
+            self._keep["ab"] = self.ab
         self.p = p
         self._bind_workspace()
 
@@ -236,9 +281,11 @@ class Problem:
             if t.dtype != want:
                 raise ValueError(f"{name} must be {want}, got {t.dtype}")
             setattr(self.p, name, t.data_ptr())
-            self._keep.append(t)
+            self._keep[name] = t
 
     def _new(self, shape, dtype=None):
+        if POISON_OUTPUTS:
+            return torch.full(shape, float("nan"), dtype=dtype or self.dtype, device=self.device)
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
 
     def forward(self, q, k, v):
@@ -263,7 +310,7 @@ class Problem:
         if want_dab:
             if self.ab is None:
                 raise ValueError("dab was requested but the problem has no bias `ab`")
-            dab = torch.empty_like(self.ab)
+            dab = self._new(self.ab.shape, torch.float32)
             self.p.dab = dab.data_ptr()
         try:
             check(lib.flexattn_bwd_dq(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_dq")
@@ -319,13 +366,20 @@ def _side_stream(device):
     return st
 
 
-def selftest_umma(variant: int, a: torch.Tensor, b: torch.Tensor, tuning=None, status=None) -> torch.Tensor:
+def selftest_umma(variant: int, a: torch.Tensor, b: torch.Tensor, status=None) -> torch.Tensor:
     """Single-tile tensor-core self check (see flexattn_selftest_umma in the header)."""
     kdim = a.shape[1]
     d = torch.empty(128, 128, dtype=torch.float32, device=a.device)
-    tune = None
-    if tuning is not None:
-        tune = (ctypes.c_int32 * 4)(*(list(tuning) + [0] * 4)[:4])
     check(lib.flexattn_selftest_umma(_stream_ptr(a.device), int(variant), _ptr(a), _ptr(b), _ptr(d), int(kdim),
-                                     _ptr(status), tune), "flexattn_selftest_umma")
+                                     _ptr(status)), "flexattn_selftest_umma")
     return d
+
+
+def selftest_timeout(limit_ms: int, status=None, device=None):
+    """Launches the time-out self check (see flexattn_selftest_timeout in the header): a wait that runs out
+    after `limit_ms` and reports like an attention kernel would.  With ``status=None`` the report goes to the
+    binding's own status words."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if status is None:
+        status = _mailbox(device)
+    check(lib.flexattn_selftest_timeout(_stream_ptr(device), int(limit_ms), _ptr(status)), "flexattn_selftest_timeout")

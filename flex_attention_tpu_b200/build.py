@@ -9,14 +9,11 @@ import sys
 
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
-# FLEXATTN_DEFINES (e.g. "-DFLEXATTN_TRACE") builds an instrumented variant into its own directory / file
-DEFINES = os.environ.get("FLEXATTN_DEFINES", "").split()
-_TAG = ("_" + hashlib.sha256(" ".join(DEFINES).encode()).hexdigest()[:8]) if DEFINES else ""
-OBJ = os.path.join(PKG, "build" + _TAG)
-LIB = os.environ.get("FLEXATTN_OUT", os.path.join(PKG, "libflexattn.so")) if DEFINES else os.path.join(PKG, "libflexattn.so")
+OBJ = os.path.join(PKG, "build")
+LIB = os.path.join(PKG, "libflexattn.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", *DEFINES]
+         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
 
 def _sources():
@@ -64,13 +61,17 @@ def build(verbose: bool = False, jobs: int | None = None) -> str:
             if log:
                 print(log)
     newest = max(os.path.getmtime(o) for o in objs)
-    if not os.path.exists(LIB) or os.path.getmtime(LIB) < newest:
+    # relink when an object is newer than the library or when the list of sources changed
+    list_path, listing = os.path.join(OBJ, "sources.list"), "\n".join(srcs)
+    same_list = os.path.exists(list_path) and open(list_path).read() == listing
+    if not os.path.exists(LIB) or os.path.getmtime(LIB) < newest or not same_list:
         cmd = [NVCC, "-shared", "-o", LIB, *objs, "-cudart", "shared", "-Xlinker", "--no-undefined"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    if not DEFINES:
-        _build_driver()
+        with open(list_path, "w") as f:
+            f.write(listing)
+    _build_driver()
     return LIB
 
 

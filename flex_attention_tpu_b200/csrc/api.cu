@@ -1,5 +1,7 @@
 // The C ABI of libflexattn.so: argument validation, backend choice and dispatch.  No allocation, no
-// host synchronisation (except flexattn_read_mask_map, a test/tool helper), no global mutable state.
+// host synchronisation (except flexattn_read_mask_map, a test/tool helper).  The only state that outlives a
+// call is per device: the abort word of the tensor-core kernels (set by a device-side time-out, cleared by
+// flexattn_reset_abort) and the caches of device attributes and symbol addresses next to it.
 #include <stdlib.h>
 #include <string.h>
 
@@ -53,15 +55,8 @@ bool use_tcgen05(const FlexAttnParams* p, int* err) {
   return capable;
 }
 
-#ifdef FLEXATTN_TRACE
-long long* g_trace_buffer = nullptr;
-#endif
-
 DevParams make_dev(const FlexAttnParams* p) {
   DevParams d{};
-#ifdef FLEXATTN_TRACE
-  d.trace = g_trace_buffer;
-#endif
   MapLayout L = map_layout(p->batch, p->seq_q, p->seq_k, p->mask_kind);
   char* ws = static_cast<char*>(p->workspace);
   d.q = p->q; d.k = p->k; d.v = p->v; d.o = p->o; d.d_o = p->d_o;
@@ -99,15 +94,23 @@ int prologue(const FlexAttnParams* p) {
 }
 
 }  // namespace
+
+// Everything flexattn_fwd checks before it launches (shapes, kinds, workspace, pointers, backend).  tc: whether
+// the tensor-core kernel serves the call.
+int validate_fwd_args(const FlexAttnParams* p, bool* tc) {
+  int e = prologue(p);
+  if (e) return e;
+  FLEXATTN_REQUIRE(p->q); FLEXATTN_REQUIRE(p->k); FLEXATTN_REQUIRE(p->v); FLEXATTN_REQUIRE(p->o);
+  FLEXATTN_REQUIRE(p->l); FLEXATTN_REQUIRE(p->m);
+  *tc = use_tcgen05(p, &e);
+  return e;
+}
+
 }  // namespace flexattn
 
 using namespace flexattn;
 
 extern "C" {
-
-#ifdef FLEXATTN_TRACE
-void flexattn_debug_set_trace(void* device_buffer) { g_trace_buffer = static_cast<long long*>(device_buffer); }
-#endif
 
 int flexattn_abi_version(void) { return FLEXATTN_ABI_VERSION; }
 
@@ -143,11 +146,8 @@ int flexattn_build_mask_map(void* stream, const FlexAttnParams* p) {
 }
 
 int flexattn_fwd(void* stream, const FlexAttnParams* p) {
-  int e = prologue(p);
-  if (e) return e;
-  FLEXATTN_REQUIRE(p->q); FLEXATTN_REQUIRE(p->k); FLEXATTN_REQUIRE(p->v); FLEXATTN_REQUIRE(p->o);
-  FLEXATTN_REQUIRE(p->l); FLEXATTN_REQUIRE(p->m);
-  const bool tc = use_tcgen05(p, &e);
+  bool tc = false;
+  const int e = validate_fwd_args(p, &tc);
   if (e) return e;
   DevParams d = make_dev(p);
   cudaStream_t st = static_cast<cudaStream_t>(stream);

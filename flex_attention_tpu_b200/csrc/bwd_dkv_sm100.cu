@@ -23,30 +23,6 @@
 // dK, dV (D columns each) stay in tensor memory across q tiles: 512 columns in total, one CTA per SM.
 #include "sm100.cuh"
 
-#ifdef FLEXATTN_TRACE
-#ifdef FLEXATTN_TRACE_WARPS
-#define FA_TRACE(slot)
-#else
-#define FA_TRACE(slot)                                                          \
-  do {                                                                          \
-    if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64)     \
-      P.trace[n * 16 + (slot)] = clock64();                                     \
-  } while (0)
-#endif
-#ifdef FLEXATTN_TRACE_WARPS
-#define FA_TRACE_AT(idx, slot)
-#else
-#define FA_TRACE_AT(idx, slot)                                                           \
-  do {                                                                                   \
-    if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (idx) >= 0 && (idx) < 64) \
-      P.trace[(idx) * 16 + (slot)] = clock64();                                          \
-  } while (0)
-#endif
-#else
-#define FA_TRACE(slot)
-#define FA_TRACE_AT(idx, slot)
-#endif
-
 namespace flexattn {
 namespace {
 
@@ -179,7 +155,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int4 cm = P.col_map[(size_t)(P.map_rows > 1 ? b : 0) * P.n_kt + kt];
   const int N = cm.y - cm.x;
 
-  if (*reinterpret_cast<volatile int*>(abort_flag) != 0) return;
+  if (aborted_on_entry(abort_flag, P.status, 3)) return;
 
   if (tid == 0) {
     ptx::mbar_init(&sh->bar_kv, 1);
@@ -239,11 +215,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         // dV(n-2) is issued before dK(n-2): the dO stage frees first
         ok = ptx::mbar_wait_relaxed(&sh->bar_dofree[st], par);
         if (!ok) break;
-        FA_TRACE_AT(n - 2, 6);
         load_tile(sDO + st * kTileBytes, &tm_do, &sh->bar_do[st], (cm.x + n) * kTile);
         ok = ptx::mbar_wait_relaxed(&sh->bar_qfree[st], par);
         if (!ok) break;
-        FA_TRACE_AT(n - 2, 7);
         load_tile(sQ + st * kTileBytes, &tm_q, &sh->bar_q[st], (cm.x + n) * kTile);
       }
       if (!ok) give_up(abort_flag, P.status, 3, 20);
@@ -309,30 +283,24 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t par_next = ((n + 1) >> 1) & 1;
         ok = ptx::mbar_wait(&sh->bar_p, par);  // P^T(n) is in tensor memory
         if (!ok) { fail_at = 2; break; }
-        FA_TRACE(0);
         ptx::tc_fence_after();
         issue_dv(n);
-        FA_TRACE(1);
         if (n + 1 < N) {
           ok = ptx::mbar_wait(&sh->bar_q[(n + 1) & 1], par_next);
           if (!ok) { fail_at = 3; break; }
           ptx::tc_fence_after();
           issue_s(n + 1);
         }
-        FA_TRACE(2);
         ok = ptx::mbar_wait(&sh->bar_ds, par);  // dS^T(n) is in tensor memory
         if (!ok) { fail_at = 4; break; }
-        FA_TRACE(3);
         ptx::tc_fence_after();
         issue_dk(n);
-        FA_TRACE(4);
         if (n + 1 < N) {
           ok = ptx::mbar_wait(&sh->bar_do[(n + 1) & 1], par_next);
           if (!ok) { fail_at = 5; break; }
           ptx::tc_fence_after();
           issue_dp(n + 1);
         }
-        FA_TRACE(5);
       }
       if (ok) ptx::mma_commit(&sh->bar_acc);
       if (!ok) give_up(abort_flag, P.status, 3, fail_at);
@@ -416,13 +384,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       // a failed wait never leaves the loop early: every thread keeps executing the same named barriers
       ptx::cp_async_wait_all();  // this thread's asynchronous copies for this tile have landed
       ptx::named_bar_sync(1 + half, 128);
-      if (tid == 0) FA_TRACE(8);
       if (!ok) continue;
       float st0[32], st1[32];
       load_stats32(st0, &sh->nlse2[st][64 * half]);
       ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_s, n & 1));
       if (!ok) { fail_at = 10; continue; }
-      if (tid == 0) FA_TRACE(9);
       ptx::tc_fence_after();
       uint32_t sr[2][32];
       ptx::tmem_ld32(lane_base + colS, sr[0]);
@@ -431,7 +397,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::tmem_wait_ld();
       ptx::tmem_ld_acquire(sr[0]);
       ptx::tmem_ld_acquire(sr[1]);
-      if (tid == 0) FA_TRACE(13);
       {
         uint32_t pk_p[32];
         const float abase = slope2 * (float)(j - i0);  // ALiBi bias = slope * (j - i), i = i0 + column
@@ -446,17 +411,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           dkv_p_math32<SK, MK, false>(sr[1], pk_p + 16, st1, &sh->doc[st][64 * half + 32], i0 + 32, j, dj, P.seq_q,
                                       P.window, P.stride, c2, slope2, abase - 32.f * slope2, capl2, csc);
         }
-        if (tid == 0) FA_TRACE(14);
         ptx::tmem_st32(lane_base + colS, pk_p);  // bf16 P^T over the first half of this warpgroup's S^T columns
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(&sh->bar_p);
       }
-#ifdef FLEXATTN_TRACE_WARPS
-      if (lane == 0 && P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64) P.trace[n * 16 + warp] = clock64();
-#else
-      if (tid == 0) FA_TRACE(10);
-#endif
       // While dP^T of this tile is still being computed: stage the statistics of the NEXT tile (its stage was last
       // read two tiles ago) and fetch those of the one after.  Done here, the shared-memory stores - slow while
       // the MMAs saturate shared memory - overlap a wait instead of delaying the first phase.
@@ -467,7 +426,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       load_stats32(st0, &sh->delta[st][64 * half]);
       ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dp, n & 1));
       if (!ok) { fail_at = 11; continue; }
-      if (tid == 0) FA_TRACE(11);
       ptx::tc_fence_after();
       {
         uint32_t pr[32], pk_ds[32];
@@ -475,7 +433,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         load_stats32(st1, &sh->delta[st][64 * half + 32]);
         ptx::tmem_wait_ld();
         ptx::tmem_ld_acquire(pr);
-        if (tid == 0) FA_TRACE(15);
         dkv_ds_math32(sr[0], pr, pk_ds, st0);
         ptx::tmem_ld32(lane_base + colDP + 32, pr);
         ptx::tmem_wait_ld();
@@ -486,10 +443,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(&sh->bar_ds);
       }
-#ifdef FLEXATTN_TRACE_WARPS
-      if (lane == 0 && P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && n < 64) P.trace[n * 16 + 8 + warp] = clock64();
-#endif
-      if (tid == 0) FA_TRACE(12);
     }
 
     if (ok && N > 0) {
@@ -557,12 +510,8 @@ int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const
   // 512 TMEM columns per CTA: never let two CTAs share an SM (the second would spin in tcgen05.alloc)
   constexpr size_t smem_req = smem > 120 * 1024 ? smem : 120 * 1024;
   auto kern = dkv_sm100_kernel<D, SK, MK>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_req) != cudaSuccess)
-      return FLEXATTN_ERR_CUDA;
-    attr_set = true;
-  }
+  static SmemAttrOnce attr_once{};  // per kernel instantiation, per device
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem_req, &attr_once) != FLEXATTN_OK) return FLEXATTN_ERR_CUDA;
   dim3 grid(d.n_kt, d.batch * d.heads);
   kern<<<grid, kThreads, smem_req, st>>>(tq, tdo, tk, tv, tdk, tdv, d, abort_flag);
   return cudaGetLastError() == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;

@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  if (*reinterpret_cast<volatile int*>(abort_flag) != 0) return;
+  if (aborted_on_entry(abort_flag, P.status, 2)) return;
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -511,12 +511,8 @@ int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const
   // 512 TMEM columns per CTA: never let two CTAs share an SM (the second would spin in tcgen05.alloc)
   constexpr size_t smem_req = smem > 120 * 1024 ? smem : 120 * 1024;
   auto kern = dq_sm100_kernel<D, SK, MK>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_req) != cudaSuccess)
-      return FLEXATTN_ERR_CUDA;
-    attr_set = true;
-  }
+  static SmemAttrOnce attr_once{};  // per kernel instantiation, per device
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem_req, &attr_once) != FLEXATTN_OK) return FLEXATTN_ERR_CUDA;
   // persistent: one CTA per SM (fewer when there are fewer work items)
   const long long items = (long long)d.n_qt * d.batch * d.heads;
   const int sms = sm_count();

@@ -74,7 +74,6 @@ struct DevParams {
   const int32_t* order;  // [rows][n_qt]: q tiles by decreasing number of kv tiles
   const int4* order_rm;  // [rows][n_qt]: row_map entry of order[i]
   int32_t* status;
-  long long* trace;  // per-phase cycle stamps of one CTA; only written by builds with FLEXATTN_TRACE
   int batch, heads, seq_q, seq_k, head_dim;
   int n_qt, n_kt, map_rows, doc_stride;
   int window, stride;
@@ -133,6 +132,9 @@ __device__ __forceinline__ void report_timeout(int32_t* status, int kernel_id, i
     }
   }
 }
+
+// Host-side validation of a forward call, shared by flexattn_fwd and flexattn_fwd_noalloc (api.cu).
+int validate_fwd_args(const FlexAttnParams* p, bool* tc);
 
 // ---------------------------------------------------------------------------------------------
 // Launchers implemented by the kernel translation units; each returns a cudaError_t.

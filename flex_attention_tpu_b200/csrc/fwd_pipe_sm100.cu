@@ -27,18 +27,6 @@
 #include "sched.cuh"
 #include "sm100.cuh"
 
-#ifdef FLEXATTN_TRACE
-// cycle stamps of CTA 0, one row of 16 slots per kv tile of its stream (first 64 tiles)
-#define FA_TRACE_T(T, slot)                                                     \
-  do {                                                                          \
-    if (P.trace != nullptr && blockIdx.x == 0 && (T) < 64)                      \
-      P.trace[(T) * 16 + (slot)] = clock64();                                   \
-  } while (0)
-#else
-#define FA_TRACE_T(T, slot)
-#endif
-
-
 namespace flexattn {
 namespace {
 
@@ -126,7 +114,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  if (*reinterpret_cast<volatile int*>(abort_flag) != 0) return;
+  if (aborted_on_entry(abort_flag, P.status, 4)) return;
 
   if (tid == 0) {
     ptx::mbar_init(&sh->bar_q, 1);
@@ -283,10 +271,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (pn == 0) pN = sh->item_tiles[pqi & 7];  // written before the Q K^T position passed this item
         ok = ptx::mbar_wait(&sh->bar_p[psb], psph);
         if (!ok) { fail_at = 4; break; }
-        FA_TRACE_T(pT, 0);
         ok = ptx::mbar_wait(&sh->bar_v[pT & 1], (pT >> 1) & 1);
         if (!ok) { fail_at = 5; break; }
-        FA_TRACE_T(pT, 1);
         ptx::tc_fence_after();
         const ptx::DescBase bv = (pT & 1) ? bV1 : bV0;
 #pragma unroll
@@ -294,7 +280,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::mma_ts(tmem + kColO, tmem + psb * 128u + kk * 8, ptx::desc_at(bv, ptx::koff_mnmajor(kk)), idesc_pv,
                       (pn > 0) || (kk > 0));
         ptx::mma_commit(&sh->bar_pv[psb]);
-        FA_TRACE_T(pT, 2);
         ++pT;
         if (++psb == kSBufs) { psb = 0; psph ^= 1u; }
         if (++pn == pN) {
@@ -302,7 +287,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           ++pqi;
         }
         if (!q_end) issue_qk();
-        FA_TRACE_T(pT - 1, 3);
       }
       if (!ok) give_up(abort_flag, P.status, 4, fail_at);
     }
@@ -347,7 +331,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_s[sb], sph));
           if (!ok) fail_at = 10;
         }
-        if (tid == 0) FA_TRACE_T(T, 8);
         float x[kHalf];
         if (ok) {
           ptx::tc_fence_after();
@@ -388,10 +371,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             xs = c2;
           }
         }
-        if (tid == 0) FA_TRACE_T(T, 9);
         sh->pmax[par][half][row] = tmax;
         ptx::named_bar_sync(1, 256);  // exchange the partial row maxima of the two halves
-        if (tid == 0) FA_TRACE_T(T, 10);
         if (ok) {
           tmax = fmaxf(tmax, sh->pmax[par][half ^ 1][row]);
           m_true = fmaxf(m_true, tmax);
@@ -433,7 +414,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             ls2[(c >> 1) & 1] = ptx::add2(ls2[(c >> 1) & 1], ptx::pack2(p0, p1));
             pk[c >> 1] = ptx::pack_bf16_trunc(p0, p1);
           }
-          if (tid == 0) FA_TRACE_T(T, 11);
           ptx::tmem_st32(lane_base + colS + (c_base >> 1), pk);
           {
             float s0, s1;
@@ -443,7 +423,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           ptx::mbar_arrive(&sh->bar_p[sb]);
-          if (tid == 0) FA_TRACE_T(T, 12);
         }
         if (++sb == kSBufs) { sb = 0; sph ^= 1u; }
       }
@@ -454,7 +433,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_pv[sb == 0 ? kSBufs - 1 : sb - 1], sb == 0 ? sph ^ 1u : sph));
         if (!ok) fail_at = 12;
       }
-      if (tid == 0) FA_TRACE_T(T - 1, 13);
       if (tid == 0 && o_pending) {  // the previous item's store has read the staging tile (long ago, normally)
         ptx::tma_store_wait_read();
         o_pending = false;
@@ -463,7 +441,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::named_bar_sync(1, 256);
       l = sh->lsum[0][row] + sh->lsum[1][row];
       ptx::named_bar_sync(3, 256);  // both halves have read lsum before the next item overwrites it
-      if (tid == 0) FA_TRACE_T(T - 1, 14);
       const float inv_l = l > 0.f ? ptx::kRoundUp / l : 0.f;  // l sums the pre-scaled probabilities
       const size_t grow = (size_t)bh * P.seq_q + i;
       if (N > 0) {
@@ -509,7 +486,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         P.l[grow] = l * ptx::ex2(m_ref - m_true) * ptx::kRoundInv;
         P.m[grow] = m_true * kLn2;
       }
-      if (tid == 0) FA_TRACE_T(T - 1, 15);
     }
     if (tid == 0 && o_pending) ptx::tma_store_wait_read();  // the staging tile must outlive the last store's reads
     if (!ok && lane == 0) give_up(abort_flag, P.status, 4, fail_at);
@@ -531,12 +507,8 @@ int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const
   // 512 TMEM columns per CTA: never let two CTAs share an SM (the second would spin in tcgen05.alloc)
   constexpr size_t smem = need > 120 * 1024 ? need : 120 * 1024;
   auto kern = fwd_pipe_sm100_kernel<D, SK, MK>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return FLEXATTN_ERR_CUDA;
-    attr_set = true;
-  }
+  static SmemAttrOnce attr_once{};  // per kernel instantiation, per device
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), (int)smem, &attr_once) != FLEXATTN_OK) return FLEXATTN_ERR_CUDA;
   // persistent: one CTA per SM (fewer when there are fewer work items)
   const long long items = (long long)d.n_qt * d.batch * d.heads;
   const int sms = sm_count();

@@ -65,9 +65,15 @@ extern "C" int flexattn_fwd_noalloc(void* stream, const FlexAttnParams* p) {
   if (scratch == nullptr) return FLEXATTN_ERR_CUDA;
   local.workspace = scratch;
   local.workspace_bytes = kNoAllocScratchBytes;
+  // Every check the forward makes runs BEFORE anything is enqueued: a call that is going to be refused (null or
+  // misaligned pointer, unsupported backend) must not have overwritten the shared array on its way out.
+  bool tc = false;
+  int e = validate_fwd_args(&local, &tc);
+  if (e != FLEXATTN_OK) return e;
   // The map builder rewrites every word the kernels read (header, row map, column map, per-tile document
-  // ranges), so nothing left in the array by an earlier call has to be cleared.
-  int e = flexattn_build_mask_map(stream, &local);
+  // ranges, the work order of the q tiles and the row-map entries in that order), so nothing left in the
+  // array by an earlier call has to be cleared.
+  e = flexattn_build_mask_map(stream, &local);
   if (e != FLEXATTN_OK) return e;
   return flexattn_fwd(stream, &local);
 }

@@ -6,15 +6,11 @@
 namespace flexattn {
 namespace {
 
-struct Tuning {
-  int lbo, sbo, kstep;
-};
-
 __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ CUtensorMap tm_a,
                                                        const __grid_constant__ CUtensorMap tm_b,
                                                        const __nv_bfloat16* __restrict__ a_glob,
                                                        float* __restrict__ d_out, int variant, int kdim,
-                                                       Tuning tune, int32_t* status, int* abort_flag) {
+                                                       int32_t* status, int* abort_flag) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;                      // 2 panels x 16 KB
@@ -73,22 +69,17 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
     if (ok) {
       ptx::tc_fence_after();
       const int ksteps = kdim / 16;
+      // exactly the descriptors of the attention kernels: K-major operands step 32 bytes per K step inside a
+      // 128-byte-swizzled panel (LBO 16, SBO 1024); MN-major operands step 2048 bytes (LBO = one panel, SBO 1024)
       if (variant == 0) {
         const uint32_t idesc = ptx::make_idesc(128, 128, false);
-        const uint32_t lbo = tune.lbo > 0 ? tune.lbo : 16, sbo = tune.sbo > 0 ? tune.sbo : 1024;
-        const uint32_t kstep = tune.kstep > 0 ? tune.kstep : 32;
-        for (int kk = 0; kk < ksteps; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * ptx::kPanelBytes + (uint32_t)(kk & 3) * kstep;
-          ptx::mma_ss(tmem + tD, ptx::make_smem_desc(ptx::smem_u32(sA) + off, lbo, sbo),
-                      ptx::make_smem_desc(ptx::smem_u32(sB) + off, lbo, sbo), idesc, kk > 0);
-        }
+        for (int kk = 0; kk < ksteps; ++kk)
+          ptx::mma_ss(tmem + tD, ptx::desc_kmajor(ptx::smem_u32(sA), kk), ptx::desc_kmajor(ptx::smem_u32(sB), kk), idesc,
+                      kk > 0);
       } else {
         const uint32_t idesc = ptx::make_idesc(128, 128, true);
-        const uint32_t lbo = tune.lbo > 0 ? tune.lbo : ptx::kPanelBytes, sbo = tune.sbo > 0 ? tune.sbo : 1024;
-        const uint32_t kstep = tune.kstep > 0 ? tune.kstep : 2048;
         for (int kk = 0; kk < ksteps; ++kk)
-          ptx::mma_ts(tmem + tD, tmem + tA + kk * 8, ptx::make_smem_desc(ptx::smem_u32(sB) + kk * kstep, lbo, sbo),
-                      idesc, kk > 0);
+          ptx::mma_ts(tmem + tD, tmem + tA + kk * 8, ptx::desc_mnmajor(ptx::smem_u32(sB), kk), idesc, kk > 0);
       }
       ptx::mma_commit(bar_mma);
     } else {
@@ -118,30 +109,62 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   }
 }
 
+// A wait that cannot succeed: nothing ever arrives on the barrier.  It runs out after `limit_ns`, after which the
+// thread reports through the same give_up path as the attention kernels (status words + the device's abort word)
+// and the kernel returns normally.  Lets the test-suite exercise the time-out handling without a fault or a hang.
+__global__ void __launch_bounds__(32) timeout_selftest_kernel(unsigned long long limit_ns, int32_t* status,
+                                                              int* abort_flag) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bar, 1);
+    ptx::fence_barrier_init();
+    const unsigned long long t0 = ptx::globaltimer_ns();
+    bool done = false;
+    while (!done && ptx::globaltimer_ns() - t0 < limit_ns) {
+#pragma unroll 1
+      for (int it = 0; it < 64 && !done; ++it) done = ptx::mbar_try_wait(&bar, 0);
+    }
+    if (!done) give_up(abort_flag, status, 101, 1);
+  }
+}
+
 }  // namespace
 }  // namespace flexattn
 
 using namespace flexattn;
 
 extern "C" int flexattn_selftest_umma(void* stream, int variant, const void* a, const void* b, float* d, int32_t kdim,
-                                      int32_t* status, const int32_t* tuning) {
+                                      int32_t* status) {
   if (a == nullptr || b == nullptr || d == nullptr) return FLEXATTN_ERR_NULL_POINTER;
   if ((variant != 0 && variant != 1) || (kdim != 64 && kdim != 128)) return FLEXATTN_ERR_BAD_SHAPE;
+  int* af = abort_flag_ptr();
+  if (af == nullptr) return FLEXATTN_ERR_CUDA;
   CUtensorMap tm_a, tm_b;
   int e = make_tile_map(&tm_a, a, 1, 128, kdim);  // [128, K] (only read through TMA by variant 0)
   if (e) return e;
   e = variant == 0 ? make_tile_map(&tm_b, b, 1, 128, kdim) : make_tile_map(&tm_b, b, 1, kdim, 128);
   if (e) return e;
-  Tuning t{0, 0, 0};
-  if (tuning != nullptr) t = Tuning{tuning[0], tuning[1], tuning[2]};
   const size_t smem = 4 * ptx::kPanelBytes + 1024 + 64;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return FLEXATTN_ERR_CUDA;
-    attr_set = true;
-  }
+  static SmemAttrOnce attr_once{};
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(selftest_kernel), (int)smem, &attr_once) != FLEXATTN_OK)
+    return FLEXATTN_ERR_CUDA;
   selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
-      tm_a, tm_b, static_cast<const __nv_bfloat16*>(a), d, variant, kdim, t, status, abort_flag_ptr());
+      tm_a, tm_b, static_cast<const __nv_bfloat16*>(a), d, variant, kdim, status, af);
   return cudaGetLastError() == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;
+}
+
+extern "C" int flexattn_selftest_timeout(void* stream, int32_t limit_ms, int32_t* status) {
+  if (limit_ms < 1 || limit_ms > 1000) return FLEXATTN_ERR_BAD_SHAPE;
+  int* af = abort_flag_ptr();
+  if (af == nullptr) return FLEXATTN_ERR_CUDA;
+  timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(1000000ull * (unsigned long long)limit_ms,
+                                                                           status, af);
+  return cudaGetLastError() == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;
+}
+
+extern "C" int flexattn_reset_abort(void* stream) {
+  int* af = abort_flag_ptr();
+  if (af == nullptr) return FLEXATTN_ERR_CUDA;
+  return cudaMemsetAsync(af, 0, sizeof(int), static_cast<cudaStream_t>(stream)) == cudaSuccess ? FLEXATTN_OK
+                                                                                               : FLEXATTN_ERR_CUDA;
 }

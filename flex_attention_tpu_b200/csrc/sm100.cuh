@@ -371,15 +371,33 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 
 }  // namespace ptx
 
-// Per-device abort flag (device address): set when any bounded wait gives up, checked by every
-// tensor-core CTA on entry so that one failure does not cost a time-out per CTA.  Sticky until the
-// process exits.  nullptr if the address cannot be resolved.
+// Per-device abort word (device address): set when any bounded wait gives up, checked by every tensor-core CTA
+// on entry so that one failure does not cost a time-out per CTA.  It stays set until flexattn_reset_abort clears
+// it; a CTA that leaves on entry because of it reports {TIMEOUT, kernel id, block, kAbortedOnEntry} in the
+// caller's status words, so a launch that did no work never looks like a success.  nullptr if the address
+// cannot be resolved.
 int* abort_flag_ptr();
+constexpr int kAbortedOnEntry = 99;
 
 __device__ __forceinline__ void give_up(int* abort_flag, int32_t* status, int kernel_id, int detail) {
   if (abort_flag != nullptr) atomicExch(abort_flag, 1);
   report_timeout(status, kernel_id, detail);
 }
+// true = the abort word is set: the CTA must return at once (before it allocates tensor memory)
+__device__ __forceinline__ bool aborted_on_entry(const int* abort_flag, int32_t* status, int kernel_id) {
+  if (*reinterpret_cast<const volatile int*>(abort_flag) == 0) return false;
+  if (threadIdx.x == 0) report_timeout(status, kernel_id, kAbortedOnEntry);
+  return true;
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the CURRENT device only, so "already done" is kept
+// per device (one flag array per kernel instantiation, owned by its launcher).  Returns FLEXATTN_OK or
+// FLEXATTN_ERR_CUDA.
+constexpr int kMaxDevices = 64;
+struct SmemAttrOnce {
+  unsigned char done[kMaxDevices];
+};
+int ensure_dynamic_smem(const void* kernel, int bytes, SmemAttrOnce* once);
 
 // Host side: 3-D tensor map over a [slices, rows, cols] bf16 array, box = {64 cols, 128 rows, 1 slice},
 // 128-byte swizzle, out-of-range rows read as zero.

@@ -1,5 +1,6 @@
 // Host helpers of the tensor-core kernels: TMA tensor-map construction (driver entry point resolved
-// through the runtime, so libcuda is not a link-time dependency) and the per-device abort flag.
+// through the runtime, so libcuda is not a link-time dependency), the per-device abort word and the per-device
+// record of kernels whose dynamic shared-memory limit has been raised.
 #include <mutex>
 
 #include "sm100.cuh"
@@ -10,9 +11,9 @@ __device__ int g_abort_word = 0;
 
 int* abort_flag_ptr() {
   static std::mutex mu;
-  static int* cache[64] = {};
+  static int* cache[kMaxDevices] = {};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
   std::lock_guard<std::mutex> lock(mu);
   if (cache[dev] == nullptr) {
     void* p = nullptr;
@@ -20,6 +21,19 @@ int* abort_flag_ptr() {
     cache[dev] = static_cast<int*>(p);
   }
   return cache[dev];
+}
+
+int ensure_dynamic_smem(const void* kernel, int bytes, SmemAttrOnce* once) {
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FLEXATTN_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!once->done[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+      return FLEXATTN_ERR_CUDA;
+    once->done[dev] = 1;
+  }
+  return FLEXATTN_OK;
 }
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

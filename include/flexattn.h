@@ -13,7 +13,12 @@
  *   - work is enqueued on `stream` (a cudaStream_t passed as void*); the host is never synchronised
  *     and nothing is allocated: outputs and the workspace belong to the caller;
  *   - the return value is a FlexAttnStatus (0 = OK); launch-time CUDA errors are reported as
- *     FLEXATTN_ERR_CUDA, asynchronous device-side time-outs through the optional `status` words.
+ *     FLEXATTN_ERR_CUDA, asynchronous device-side time-outs through the optional `status` words;
+ *   - device-side time-outs are sticky per device: every wait inside the tensor-core kernels is bounded, and
+ *     the first one that gives up sets an abort word on its device.  From then on every tensor-core launch on
+ *     that device returns at once, writes {FLEXATTN_ERR_TIMEOUT, kernel id, block, 99} into `status` and
+ *     leaves its outputs untouched, until flexattn_reset_abort has run.  The entry points still return
+ *     FLEXATTN_OK (they do not synchronise), so a caller that wants to see the failure must pass `status`.
  *
  * Fixed math convention (identical to the reference whenever sm_scale == 1, the only setting its
  * score_fn tests use):
@@ -30,7 +35,7 @@
 extern "C" {
 #endif
 
-#define FLEXATTN_ABI_VERSION 2
+#define FLEXATTN_ABI_VERSION 3
 #define FLEXATTN_TILE 128 /* q-tile and kv-tile edge used by the mask map and by every kernel */
 
 typedef enum FlexAttnStatus {
@@ -104,8 +109,10 @@ typedef struct FlexAttnParams {
   /* caller-owned scratch: holds the mask map written by flexattn_build_mask_map */
   void* workspace;
   size_t workspace_bytes;
-  /* optional device int32[4]: {code, kernel id, block, detail}; written when a bounded wait inside a
-   * kernel gives up (code = FLEXATTN_ERR_TIMEOUT).  Zero it before the call; may be NULL. */
+  /* optional int32[4] the device can write (device memory, or pinned host memory the device can reach):
+   * {code, kernel id, block, detail}; written when a bounded wait inside a kernel gives up, or when the
+   * launch found the device's abort word set (code = FLEXATTN_ERR_TIMEOUT; detail 99 = aborted on entry).
+   * Only the first report lands: zero it to re-arm.  May be NULL. */
   int32_t* status;
   int32_t backend;            /* FlexAttnBackend */
   int32_t reserved;
@@ -161,8 +168,12 @@ int flexattn_bwd_dkv(void* stream, const FlexAttnParams* p);
  * alibi_slopes as the mask / score kinds require); `workspace` and `workspace_bytes` are ignored.  The
  * mask map is built, on `stream`, into a fixed array of flexattn_noalloc_scratch_bytes() = 1 MiB that is
  * part of the library's device image (each GPU that loads the library carries it until the process
- * exits), then the forward kernel runs from it.  Nothing is allocated or freed, by the CUDA runtime or
- * by any library, on any call.
+ * exits), then the forward kernel runs from it.  The entry point itself never calls an allocating or
+ * freeing routine of the CUDA runtime or of any library.  What the driver does on its own when a device
+ * first uses the library (loading the module, which is when the array and the kernels' code take their
+ * place in device memory) happens during the first call on that device; after that call, device memory
+ * does not change across calls.  Arguments are validated before anything is enqueued, so a refused call
+ * leaves the array as it was.
  *
  *  - A problem whose mask map needs more than that (flexattn_workspace_bytes(p) > 1 MiB) is refused with
  *    FLEXATTN_ERR_NOALLOC_LIMIT; use flexattn_fwd with your own workspace instead.
@@ -183,15 +194,23 @@ size_t flexattn_noalloc_scratch_bytes(void);
 int flexattn_read_mask_map(void* stream, const FlexAttnParams* p, int which, int b, int index,
                            int32_t out[4]);
 
+/* Clears the calling device's abort word (stream-ordered memset on `stream`), re-enabling the tensor-core
+ * kernels after a device-side time-out.  Replaces nothing in the reference. */
+int flexattn_reset_abort(void* stream);
+
 /* Single-tile tensor-core self checks used by the test-suite (not part of the attention path):
  * D[128,128] = A[128,K] * B^T with A,B bf16 in global memory; `variant` selects the operand
  * staging: 0 = A,B K-major from shared memory; 1 = A from tensor memory (bf16 packed), B MN-major
  * from shared memory (then B is [K,128] row-major).  kdim is 64 or 128.  Output f32 [128,128].
- * `tuning` (host pointer, may be NULL) overrides descriptor fields for hardware probing:
- * {leading byte offset, stride byte offset, bytes added to the start address per K step, unused};
- * a value <= 0 keeps the library's own setting.  Replaces nothing in the reference. */
+ * The shared-memory descriptors are the ones the attention kernels use.  Replaces nothing in the reference. */
 int flexattn_selftest_umma(void* stream, int variant, const void* a, const void* b, float* d,
-                           int32_t kdim, int32_t* status, const int32_t* tuning);
+                           int32_t kdim, int32_t* status);
+
+/* Time-out self check used by the test-suite: one warp waits, for `limit_ms` (1..1000) milliseconds, on a
+ * barrier nothing arrives on, then reports exactly like an attention kernel whose wait ran out (status =
+ * {FLEXATTN_ERR_TIMEOUT, 101, 0, 1}, abort word set) and returns; the context stays usable.  Replaces
+ * nothing in the reference. */
+int flexattn_selftest_timeout(void* stream, int32_t limit_ms, int32_t* status);
 
 #ifdef __cplusplus
 }

@@ -2,18 +2,47 @@
 vocabulary, one call of the whole hot path through the Python entry points, and the error metrics."""
 from __future__ import annotations
 
+import json
+import os
+
 import numpy as np
 import torch
 
 from oracle import mha_reference_cpu as oracle
 
-# tolerances fixed by the build's brief: fp32 inputs max-abs <= 2e-3; bf16 inputs max-abs <= 2e-2 and
+# Tolerances fixed by the build's brief: fp32 inputs max-abs <= 2e-3; bf16 inputs max-abs <= 2e-2 and
 # max-relative (max-abs error / max-abs reference) <= 1e-2, on O, dQ, dK, dV.
-# The bf16 outputs are STORED in bf16 (the reference returns the input dtype too), and a bf16 store alone
-# moves a value r by up to half an ulp = 2^-9 * 2^ceil(log2|r|) <= 2^-8 |r|: 0.0156 for |r| in [4, 8) and
-# 0.031 for |r| in [8, 16), magnitudes the gradients reach.  The absolute bound therefore applies to the
-# error in excess of that store rounding: |t - r| - `round` * |r| <= 2e-2, element-wise.
-TOL = {torch.float32: dict(abs=2e-3, rel=None, round=0.0), torch.bfloat16: dict(abs=2e-2, rel=1e-2, round=2.0 ** -8)}
+#
+# The bf16 outputs are STORED in bf16 (the reference returns the input dtype too).  Storing a value r in bf16
+# moves it by up to half a unit in the last place, hulp(r) = 2^(e-8) for |r| in [2^e, 2^(e+1)): 0.0039 below 2,
+# 0.0078 in [2,4), 0.0156 in [4,8), 0.031 in [8,16) - magnitudes the gradients reach - so no implementation
+# that returns bf16 can meet a flat 2e-2 on such elements.  The rule asserted for bf16 is therefore
+#   (a) FLAT  |t - r| <= 2e-2 on every element with |r| < 4, where the store costs at most 0.0078 and cannot
+#       excuse anything;
+#   (b) |t - r| - n * hulp(r) <= 2e-2 on every element (n = 1 against the f32 oracle, n = 2 when the comparand
+#       is itself a bf16-stored result);
+#   (c) max|t - r| / max|r| <= 1e-2;
+# and the raw max-abs, max-rel and rel-L2 of every comparison are recorded (see `record`).
+TOL = {torch.float32: dict(abs=2e-3, rel=None, small=None), torch.bfloat16: dict(abs=2e-2, rel=1e-2, small=4.0)}
+
+
+def bf16_half_ulp(r):
+    """Half a unit in the last place of the bf16 value nearest to r (8 significand bits), element-wise."""
+    _, e = np.frexp(np.abs(np.asarray(r, np.float32)))          # |r| = f * 2^e, f in [0.5, 1)
+    return np.ldexp(np.float32(1.0), e - 9).astype(np.float32)   # 2^((e-1) - 8)
+
+
+_LOG_PATH = os.environ.get("FLEXATTN_PARITY_LOG")
+
+
+def record(case, name, e):
+    """Keeps the raw error figures of one comparison: printed (visible with pytest -rA / -s) and, when
+    FLEXATTN_PARITY_LOG names a file, appended to it as one JSON line."""
+    line = dict(case=case, output=name, **{k: float(v) for k, v in e.items()})
+    print("parity", json.dumps(line))
+    if _LOG_PATH:
+        with open(_LOG_PATH, "a") as f:
+            f.write(json.dumps(line) + "\n")
 
 
 def make_qkvdo(shape_q, shape_k, seed, dtype, device="cuda"):
@@ -81,30 +110,47 @@ def oracle_hot_path(qh, kh, vh, doh, *, sm_scale, mask_kind="none", score_kind="
     return dict(o=o, l=l, m=m, delta=oracle.delta_reference(o, doh), dq=dq, dk=dk, dv=dv)
 
 
-def errors(test, ref, round_rel=0.0):
+def errors(test, ref, roundings=0, small=None):
+    """Raw and rule-adjusted error figures of `test` against `ref`.  roundings: number of bf16 stores between
+    the two (0 for f32 results); small: the |ref| bound below which the flat tolerance applies."""
     t = test.detach().float().cpu().numpy() if isinstance(test, torch.Tensor) else np.asarray(test, np.float32)
-    r = np.asarray(ref, np.float32)
+    r = ref.detach().float().cpu().numpy() if isinstance(ref, torch.Tensor) else np.asarray(ref, np.float32)
     diff = np.abs(t - r)
-    return dict(max_abs=float(diff.max()), max_rel=float(diff.max() / max(np.abs(r).max(), 1e-30)),
-                rel_l2=float(np.linalg.norm(t - r) / (np.linalg.norm(r) + 1e-6)),
-                max_abs_excess=float((diff - round_rel * np.abs(r)).max()))
+    out = dict(max_abs=float(diff.max()), max_rel=float(diff.max() / max(np.abs(r).max(), 1e-30)),
+               rel_l2=float(np.linalg.norm((t - r).ravel().astype(np.float64)) /
+                            (np.linalg.norm(r.ravel().astype(np.float64)) + 1e-6)),
+               max_ref=float(np.abs(r).max()))
+    out["max_abs_excess"] = float((diff - roundings * bf16_half_ulp(r)).max()) if roundings else out["max_abs"]
+    if small is not None:
+        sel = np.abs(r) < small
+        out["max_abs_small"] = float(diff[sel].max()) if sel.any() else 0.0
+    return out
 
 
-def assert_close(got, want, dtype, names=("o", "dq", "dk", "dv"), what=""):
+def check_output(case, name, test, ref, dtype, roundings=None):
+    """Asserts the tolerance rule above for one output tensor and records the raw figures."""
     tol = TOL[dtype]
-    report = {}
-    for n in names:
-        e = errors(got[n], want[n], tol["round"])
-        report[n] = e
-        assert np.isfinite(e["max_abs"]), f"{what} {n}: non-finite result"
-        assert e["max_abs_excess"] <= tol["abs"], f"{what} {n}: max-abs {e['max_abs']:.3e} > {tol['abs']}  ({e})"
-        if tol["rel"] is not None:
-            assert e["max_rel"] <= tol["rel"], f"{what} {n}: max-rel {e['max_rel']:.3e} > {tol['rel']}  ({e})"
+    if roundings is None:
+        roundings = 1 if dtype == torch.bfloat16 else 0
+    e = errors(test, ref, roundings, tol["small"])
+    record(case, name, e)
+    assert np.isfinite(e["max_abs"]), f"{case} {name}: non-finite result"
+    assert e["max_abs_excess"] <= tol["abs"], f"{case} {name}: max-abs beyond store rounding {e['max_abs_excess']:.3e} > {tol['abs']}  ({e})"
+    if tol["small"] is not None:
+        assert e["max_abs_small"] <= tol["abs"], f"{case} {name}: flat max-abs on |ref| < {tol['small']}: {e['max_abs_small']:.3e} > {tol['abs']}  ({e})"
+    if tol["rel"] is not None:
+        assert e["max_rel"] <= tol["rel"], f"{case} {name}: max-rel {e['max_rel']:.3e} > {tol['rel']}  ({e})"
+    return e
+
+
+def assert_close(got, want, dtype, names=("o", "dq", "dk", "dv"), what="", roundings=None):
+    report = {n: check_output(what, n, got[n], want[n], dtype, roundings) for n in names}
     # residuals: l relative, m absolute (f32 in every dtype; the tensor-core path computes them from
     # bf16 products, hence the looser bound there)
     lm_tol = 2e-3 if dtype == torch.float32 else 2e-2
     e_m = errors(got["m"], want["m"])
     assert e_m["max_abs"] <= lm_tol, f"{what} m: {e_m}"
-    l_t, l_r = got["l"].float().cpu().numpy(), np.asarray(want["l"])
+    as_np = lambda x: x.detach().float().cpu().numpy() if isinstance(x, torch.Tensor) else np.asarray(x)
+    l_t, l_r = as_np(got["l"]), as_np(want["l"])
     assert float(np.abs(l_t / l_r - 1).max()) <= lm_tol, f"{what} l: rel {np.abs(l_t / l_r - 1).max():.3e}"
     return report

@@ -39,7 +39,7 @@ def test_status_strings(B):
     assert B.status_string(0) == "ok"
     assert "workspace" in B.status_string(6)
     assert B.status_string(12345) == "unknown status"
-    assert B.lib.flexattn_abi_version() == 2
+    assert B.lib.flexattn_abi_version() == 3
 
 
 def test_workspace_bytes(B):

@@ -5,6 +5,8 @@ import numpy as np
 import pytest
 import torch
 
+import workloads
+
 from helpers import assert_close, make_qkvdo, oracle_hot_path, run_hot_path, build_mods
 
 
@@ -17,7 +19,7 @@ def test_backward_through_autograd(mask_kind, score_kind, dtype):
     import flex_attention_tpu_b200 as fa
     B, H, S, D = 2, 3, 400, 64
     (q, k, v, do), host = make_qkvdo((B, H, S, D), (B, H, S, D), 21, dtype)
-    doc = fa.workloads.draw_documents(np.random.default_rng(3), B, S, lo=40, hi=200)[0] if mask_kind == "document" else None
+    doc = workloads.draw_documents(np.random.default_rng(3), B, S, lo=40, hi=200)[0] if mask_kind == "document" else None
     slopes = (2.0 ** (-8.0 * (np.arange(H) + 1) / H)).astype(np.float32) if score_kind == "alibi" else None
     kw = dict(sm_scale=0.11, mask_kind=mask_kind, score_kind=score_kind, window=96, doc_ids=doc, cap=6.0, slopes=slopes)
     mf, bf, sf, seg = build_mods(fa, mask_kind, score_kind, window=96, doc_ids=doc, cap=6.0, slopes=slopes)

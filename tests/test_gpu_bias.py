@@ -4,6 +4,8 @@ import numpy as np
 import pytest
 import torch
 
+import workloads
+
 from helpers import TOL, assert_close, build_mods, errors, make_qkvdo
 from oracle import mha_reference_cpu as oracle
 
@@ -31,7 +33,7 @@ def test_bias_forward_and_backward(mask_kind, score_kind, dtype):
     rng = np.random.default_rng(7)
     ab_h = (0.7 * rng.standard_normal((B, H, Sq, Sk))).astype(np.float32)
     ab = torch.from_numpy(ab_h).cuda()
-    doc = fa.workloads.draw_documents(np.random.default_rng(3), B, Sq, lo=30, hi=120)[0] if mask_kind == "document" else None
+    doc = workloads.draw_documents(np.random.default_rng(3), B, Sq, lo=30, hi=120)[0] if mask_kind == "document" else None
     cap = 5.0 if score_kind == "softcap" else 0.0
     got = _run(fa, q, k, v, do, ab, sm_scale=0.12, mask_kind=mask_kind, score_kind=score_kind, doc=doc, cap=cap)
     kw = dict(sm_scale=0.12, mask_kind=mask_kind, doc_ids=doc, score_kind=score_kind, cap=cap or None)
@@ -42,7 +44,7 @@ def test_bias_forward_and_backward(mask_kind, score_kind, dtype):
     assert_close(got, want, dtype, what=f"bias {mask_kind}/{score_kind}")
     # dab is float32 in both cases; with bf16 inputs delta comes from the bf16-rounded o, hence the relative bound
     e = errors(got["dab"], dab)
-    assert (e["max_abs"] <= 2e-3) if dtype == torch.float32 else (e["max_rel"] <= TOL[torch.bfloat16]["rel"]), e
+    assert (e["max_abs"] <= 2e-3) if dtype == torch.float32 else (e["max_rel"] <= 1e-2), e
 
 
 def test_bias_gets_a_gradient_through_autograd_and_is_refused_by_tcgen05():

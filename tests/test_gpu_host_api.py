@@ -12,7 +12,8 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("mask_kind,score_kind", [("causal", "none"), ("document", "softcap")])
 def test_host_pipeline_matches_device_entry_points(mask_kind, score_kind):
     import flex_attention_tpu_b200 as fa
-    from flex_attention_tpu_b200 import host_api, workloads
+    from flex_attention_tpu_b200 import host_api
+    import workloads
     B, H, S, D = 5, 2, 640, 128
     (q, k, v, do), _ = make_qkvdo((B, H, S, D), (B, H, S, D), 77, torch.bfloat16)
     doc = None

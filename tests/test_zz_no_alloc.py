@@ -13,7 +13,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import TOL, errors, make_qkvdo
+from helpers import check_output, make_qkvdo
 
 pytestmark = pytest.mark.gpu
 
@@ -57,9 +57,8 @@ def _run_both(B, q, k, v, **kw):
 
 def test_noalloc_forward_matches_workspace_forward_twice_in_a_row():
     from flex_attention_tpu_b200 import _binding as B
-    from flex_attention_tpu_b200 import workloads
+    import workloads
     assert B.lib.flexattn_noalloc_scratch_bytes() == 1 << 20
-    tol = TOL[torch.bfloat16]
 
     # call 1: causal, ragged length; call 2 (same array, different map layout): per-row documents + ALiBi
     (q, k, v, _), _ = make_qkvdo((2, 2, 700, 128), (2, 2, 700, 128), 41, torch.bfloat16)
@@ -70,11 +69,23 @@ def test_noalloc_forward_matches_workspace_forward_twice_in_a_row():
     (q2, k2, v2, _), _ = make_qkvdo((2, 3, 1000, 64), (2, 3, 1000, 64), 42, torch.bfloat16)
     second = _run_both(B, q2, k2, v2, mask_kind=B.MASK_DOCUMENT, score_kind=B.SCORE_ALIBI, doc=doc, slopes=slopes)
 
+    # device memory does not move across a call once the device has used the library (the first call loaded
+    # the module): free bytes are identical before and after one more call
+    o = torch.empty_like(q2); l = torch.empty(q2.shape[:3], dtype=torch.float32, device="cuda"); m = torch.empty_like(l)
+    p = _params(B, None, q2, k2, v2, o, l, m, mask_kind=B.MASK_DOCUMENT, score_kind=B.SCORE_ALIBI, doc=doc, slopes=slopes)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    assert B.lib.flexattn_fwd_noalloc(stream, ctypes.byref(p)) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
+    assert torch.equal(o, second[1][0])
+
     for (ref, got) in (first, second):
         for name, a, b in zip(("o", "l", "m"), ref, got):
             assert torch.isfinite(b.float()).all(), name
-            e = errors(b, a.float().cpu().numpy(), tol["round"])
-            assert e["max_abs_excess"] <= tol["abs"] and e["max_rel"] <= tol["rel"], (name, e)
+            check_output("noalloc vs workspace", name, b, a, torch.bfloat16 if name == "o" else torch.float32)
             assert torch.equal(a, b), f"{name}: same kernel, same inputs, different scratch location"
 
 
@@ -93,3 +104,27 @@ def test_noalloc_refuses_what_does_not_fit():
     assert B.lib.flexattn_fwd_noalloc(stream, None) == 1
     p.head_dim = 48
     assert B.lib.flexattn_fwd_noalloc(stream, ctypes.byref(p)) == 4      # ordinary validation still speaks
+
+
+def test_noalloc_refused_call_leaves_the_array_alone():
+    """A call that is refused for a bad pointer must not have rebuilt the map first: the next workspace-free
+    forward of the PREVIOUS problem's shape is not what proves it (it rebuilds), so the array is read back."""
+    from flex_attention_tpu_b200 import _binding as B
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    (q, k, v, _), _ = make_qkvdo((1, 2, 512, 128), (1, 2, 512, 128), 43, torch.bfloat16)
+    o = torch.empty_like(q); l = torch.empty(q.shape[:3], dtype=torch.float32, device="cuda"); m = torch.empty_like(l)
+    p = _params(B, None, q, k, v, o, l, m, mask_kind=B.MASK_CAUSAL)
+    assert B.lib.flexattn_fwd_noalloc(stream, ctypes.byref(p)) == 0
+    torch.cuda.synchronize()
+    good = o.clone()
+    # same shapes, another mask, but a misaligned output pointer: refused with MISALIGNED before any launch
+    bad = _params(B, None, q, k, v, o, l, m, mask_kind=B.MASK_SLIDING_WINDOW_CAUSAL, window=64)
+    bad.o = o.data_ptr() + 2
+    assert B.lib.flexattn_fwd_noalloc(stream, ctypes.byref(bad)) == 5
+    # the array still holds the causal map: run the plain forward FROM it (no rebuild) via a second no-alloc
+    # call's twin - flexattn_fwd with the library's array is not reachable from outside, so instead check that a
+    # repeated good call reproduces the result bit for bit and the refused call wrote nothing to o
+    assert torch.equal(o, good)
+    assert B.lib.flexattn_fwd_noalloc(stream, ctypes.byref(p)) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(o, good)
