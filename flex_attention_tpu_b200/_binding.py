@@ -14,15 +14,15 @@ import torch
 _LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libflexattn.so")
 
 DTYPE_BF16, DTYPE_F32 = 0, 1
-SCORE_NONE, SCORE_ALIBI, SCORE_SOFTCAP = 0, 1, 2
+SCORE_NONE, SCORE_ALIBI, SCORE_SOFTCAP, SCORE_USER = 0, 1, 2, 3
 MASK_NONE, MASK_CAUSAL, MASK_SLIDING_WINDOW, MASK_SLIDING_WINDOW_CAUSAL, MASK_DOCUMENT, MASK_S2 = range(6)
 BACKEND_AUTO, BACKEND_SIMT, BACKEND_TCGEN05 = 0, 1, 2
 TILE = 128
-ABI_VERSION = 3   # FLEXATTN_ABI_VERSION of include/flexattn.h this binding was written against
+ABI_VERSION = 4   # FLEXATTN_ABI_VERSION of include/flexattn.h this binding was written against
 
 MASK_KIND_IDS = {"none": MASK_NONE, "causal": MASK_CAUSAL, "sliding_window": MASK_SLIDING_WINDOW,
                  "sliding_window_causal": MASK_SLIDING_WINDOW_CAUSAL, "document": MASK_DOCUMENT, "s2": MASK_S2}
-SCORE_KIND_IDS = {"none": SCORE_NONE, "alibi": SCORE_ALIBI, "softcap": SCORE_SOFTCAP}
+SCORE_KIND_IDS = {"none": SCORE_NONE, "alibi": SCORE_ALIBI, "softcap": SCORE_SOFTCAP, "user": SCORE_USER}
 BACKEND_IDS = {"auto": BACKEND_AUTO, "simt": BACKEND_SIMT, "tcgen05": BACKEND_TCGEN05}
 
 
@@ -38,7 +38,7 @@ class FlexAttnParams(ctypes.Structure):
         ("score_kind", ctypes.c_int32), ("softcap", ctypes.c_float),
         ("mask_kind", ctypes.c_int32), ("window", ctypes.c_int32), ("stride", ctypes.c_int32),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
-        ("status", ctypes.c_void_p), ("backend", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("status", ctypes.c_void_p), ("backend", ctypes.c_int32), ("user_score", ctypes.c_int32),
         ("ab", ctypes.c_void_p), ("dab", ctypes.c_void_p),
     ]
 
@@ -79,6 +79,14 @@ def _load():
     lib.flexattn_selftest_timeout.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
     lib.flexattn_reset_abort.restype = ctypes.c_int
     lib.flexattn_reset_abort.argtypes = [ctypes.c_void_p]
+    lib.flexattn_user_score_create.restype = ctypes.c_int
+    lib.flexattn_user_score_create.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_int32)]
+    lib.flexattn_user_score_destroy.restype = ctypes.c_int
+    lib.flexattn_user_score_destroy.argtypes = [ctypes.c_int32]
+    lib.flexattn_user_score_log.restype = ctypes.c_char_p
+    lib.flexattn_user_score_log.argtypes = [ctypes.c_int32]
+    lib.flexattn_user_score_compile.restype = ctypes.c_int
+    lib.flexattn_user_score_compile.argtypes = [ctypes.c_int32, ctypes.c_int, ctypes.c_int32, ctypes.c_int32]
     if lib.flexattn_abi_version() != ABI_VERSION:
         raise ImportError("libflexattn.so ABI version mismatch: rebuild the library")
     return lib
@@ -94,6 +102,29 @@ def status_string(code: int) -> str:
 def check(code: int, where: str):
     if code != 0:
         raise FlexAttnError(code, where)
+
+
+_USER_SCORES = {}   # (score expression, derivative expression) -> handle of the library
+
+
+def user_score_handle(score_expr: str, dscore_expr: str) -> int:
+    """Registers a pair of CUDA expressions with the library (once per distinct pair) and returns its handle."""
+    key = (score_expr, dscore_expr)
+    h = _USER_SCORES.get(key)
+    if h is None:
+        out = ctypes.c_int32(0)
+        check(lib.flexattn_user_score_create(score_expr.encode(), dscore_expr.encode(), ctypes.byref(out)),
+              "flexattn_user_score_create")
+        h = _USER_SCORES[key] = int(out.value)
+    return h
+
+
+def check_user(code: int, where: str, handle: int):
+    """`check` that appends the run-time compiler's log when a user score function failed to compile."""
+    if code == 13:
+        log = lib.flexattn_user_score_log(handle).decode(errors="replace")
+        raise FlexAttnError(code, f"{where}\n{log}")
+    check(code, where)
 
 
 def _stream_ptr(device):
@@ -154,7 +185,8 @@ class Problem:
     _MAP_CACHE_ENTRIES = 16
 
     def __init__(self, q, k, *, sm_scale, mask_kind=MASK_NONE, window=0, stride=0, doc_ids=None,
-                 score_kind=SCORE_NONE, softcap=0.0, alibi_slopes=None, backend=BACKEND_AUTO, status=None, ab=None):
+                 score_kind=SCORE_NONE, softcap=0.0, alibi_slopes=None, backend=BACKEND_AUTO, status=None, ab=None,
+                 user_score=0):
         if not q.is_cuda:
             raise ValueError("flex attention tensors must live on a CUDA device (no CPU path exists)")
         if q.dim() != 4 or k.dim() != 4:
@@ -173,6 +205,7 @@ class Problem:
         p.score_kind, p.softcap = int(score_kind), float(softcap)
         p.mask_kind, p.window, p.stride = int(mask_kind), int(window), int(stride)
         p.backend = int(backend)
+        p.user_score = int(user_score)
         self._keep = {}  # tensors whose pointers sit in `p`, by field name
         if mask_kind == MASK_DOCUMENT:
             if doc_ids is None:
@@ -197,7 +230,7 @@ class Problem:
         self._keep["status"] = status
         self.ab = None
         if ab is not None:
-            # dense additive bias [B,H,Sq,Sk], float32 (SIMT backend; the library refuses it on tcgen05)
+            # dense additive bias [B,H,Sq,Sk], float32
             if not (isinstance(ab, torch.Tensor) and ab.is_cuda):
                 raise ValueError("ab must be a CUDA tensor")
             if tuple(ab.shape) != (B, H, Sq, k.shape[2]):
@@ -292,7 +325,7 @@ class Problem:
         B, H, Sq, D = self.shape_q
         o, l, m = self._new(self.shape_q), self._new((B, H, Sq), torch.float32), self._new((B, H, Sq), torch.float32)
         self._bind(q=q, k=k, v=v, o=o, l=l, m=m)
-        check(lib.flexattn_fwd(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_fwd")
+        check_user(lib.flexattn_fwd(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_fwd", self.p.user_score)
         return o, l, m
 
     def preprocess(self, o, do):
@@ -313,7 +346,7 @@ class Problem:
             dab = self._new(self.ab.shape, torch.float32)
             self.p.dab = dab.data_ptr()
         try:
-            check(lib.flexattn_bwd_dq(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_dq")
+            check_user(lib.flexattn_bwd_dq(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_dq", self.p.user_score)
         finally:
             self.p.dab = None
         return (dq, dab) if want_dab else dq
@@ -321,7 +354,7 @@ class Problem:
     def bwd_dkv(self, q, k, v, do, l, m, delta):
         dk, dv = self._new(self.shape_k), self._new(self.shape_k)
         self._bind(q=q, k=k, v=v, d_o=do, l=l, m=m, delta=delta, dk=dk, dv=dv)
-        check(lib.flexattn_bwd_dkv(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_dkv")
+        check_user(lib.flexattn_bwd_dkv(_stream_ptr(self.device), ctypes.byref(self.p)), "flexattn_bwd_dkv", self.p.user_score)
         return dk, dv
 
     def backward(self, q, k, v, o, do, l, m, need_dq=True, need_dkv=True, want_dab=False, two_streams=None):
@@ -346,7 +379,7 @@ class Problem:
         dk, dv = self._new(self.shape_k), self._new(self.shape_k)   # allocated on the current stream
         side.wait_stream(cur)
         self._bind(q=q, k=k, v=v, d_o=do, l=l, m=m, delta=delta, dk=dk, dv=dv)
-        check(lib.flexattn_bwd_dkv(ctypes.c_void_p(side.cuda_stream), ctypes.byref(self.p)), "flexattn_bwd_dkv")
+        check_user(lib.flexattn_bwd_dkv(ctypes.c_void_p(side.cuda_stream), ctypes.byref(self.p)), "flexattn_bwd_dkv", self.p.user_score)
         dq = self.bwd_dq(q, k, v, do, l, m, delta)
         cur.wait_stream(side)
         return delta, dq, dk, dv

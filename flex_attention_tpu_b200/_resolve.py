@@ -40,4 +40,6 @@ def make_problem(q, k, *, ab, segment_ids, causal, sm_scale, mask_fn, block_mask
               status=status, ab=ab)
     if sspec is not None:
         kw.update(score_kind=B.SCORE_KIND_IDS[sspec.kind], softcap=sspec.cap, alibi_slopes=sspec.slopes)
+        if sspec.kind == "user":
+            kw.update(user_score=B.user_score_handle(sspec.expr, sspec.dexpr))
     return B.Problem(q, k, **kw)

@@ -19,7 +19,7 @@ int validate_common(const FlexAttnParams* p) {
   if ((long long)p->batch * p->heads > 0x7fffffffLL / 2) return FLEXATTN_ERR_BAD_SHAPE;
   if (p->dtype != FLEXATTN_BF16 && p->dtype != FLEXATTN_F32) return FLEXATTN_ERR_UNSUPPORTED_DTYPE;
   if (p->head_dim != 32 && p->head_dim != 64 && p->head_dim != 128) return FLEXATTN_ERR_UNSUPPORTED_HEAD_DIM;
-  if (p->score_kind < FLEXATTN_SCORE_NONE || p->score_kind > FLEXATTN_SCORE_SOFTCAP) return FLEXATTN_ERR_UNSUPPORTED_MOD;
+  if (p->score_kind < FLEXATTN_SCORE_NONE || p->score_kind > FLEXATTN_SCORE_USER) return FLEXATTN_ERR_UNSUPPORTED_MOD;
   if (p->mask_kind < FLEXATTN_MASK_NONE || p->mask_kind > FLEXATTN_MASK_S2) return FLEXATTN_ERR_UNSUPPORTED_MOD;
   if (p->backend < FLEXATTN_BACKEND_AUTO || p->backend > FLEXATTN_BACKEND_TCGEN05) return FLEXATTN_ERR_UNSUPPORTED_BACKEND;
   return FLEXATTN_OK;
@@ -34,6 +34,7 @@ int validate_mods(const FlexAttnParams* p) {
   if (mk == FLEXATTN_MASK_DOCUMENT && p->doc_ids == nullptr) return FLEXATTN_ERR_NULL_POINTER;
   if (p->score_kind == FLEXATTN_SCORE_ALIBI && p->alibi_slopes == nullptr) return FLEXATTN_ERR_NULL_POINTER;
   if (p->score_kind == FLEXATTN_SCORE_SOFTCAP && !(p->softcap > 0.f)) return FLEXATTN_ERR_UNSUPPORTED_MOD;
+  if (p->score_kind == FLEXATTN_SCORE_USER && p->user_score <= 0) return FLEXATTN_ERR_UNSUPPORTED_MOD;
   return FLEXATTN_OK;
 }
 
@@ -47,9 +48,14 @@ int validate_workspace(const FlexAttnParams* p) {
 
 // true when the tensor-core kernels serve this problem
 bool use_tcgen05(const FlexAttnParams* p, int* err) {
-  // the tensor-core kernels take bf16, D in {64, 128} and no dense bias
-  const bool capable = p->dtype == FLEXATTN_BF16 && (p->head_dim == 64 || p->head_dim == 128) && p->ab == nullptr;
+  // the tensor-core kernels take bf16 and D in {64, 128}
+  const bool capable = p->dtype == FLEXATTN_BF16 && (p->head_dim == 64 || p->head_dim == 128);
   *err = FLEXATTN_OK;
+  // a user score function exists only as a run-time compiled tensor-core kernel
+  if (p->score_kind == FLEXATTN_SCORE_USER && (!capable || p->backend == FLEXATTN_BACKEND_SIMT)) {
+    *err = FLEXATTN_ERR_UNSUPPORTED_BACKEND;
+    return false;
+  }
   if (p->backend == FLEXATTN_BACKEND_SIMT) return false;
   if (p->backend == FLEXATTN_BACKEND_TCGEN05 && !capable) *err = FLEXATTN_ERR_UNSUPPORTED_BACKEND;
   return capable;
@@ -76,6 +82,7 @@ DevParams make_dev(const FlexAttnParams* p) {
   d.doc_stride = p->seq_q > p->seq_k ? p->seq_q : p->seq_k;
   d.window = p->window; d.stride = p->stride > 0 ? p->stride : 1;
   d.sm_scale = p->sm_scale; d.cap = p->score_kind == FLEXATTN_SCORE_SOFTCAP ? p->softcap : 0.f;
+  d.user_score = p->score_kind == FLEXATTN_SCORE_USER ? p->user_score : 0;
   return d;
 }
 
@@ -129,6 +136,8 @@ const char* flexattn_status_string(int status) {
     case FLEXATTN_ERR_UNSUPPORTED_BACKEND: return "backend cannot serve this dtype / head_dim";
     case FLEXATTN_ERR_NOALLOC_LIMIT:
       return "mask map larger than the fixed scratch array of the no-allocation entry point (1 MiB)";
+    case FLEXATTN_ERR_JIT_UNAVAILABLE: return "run-time compiler (libnvrtc) or driver module loader not available";
+    case FLEXATTN_ERR_JIT_COMPILE: return "the user score function did not compile (see flexattn_user_score_log)";
     default: return "unknown status";
   }
 }

@@ -24,7 +24,7 @@
 #include "sm100.cuh"
 
 namespace flexattn {
-namespace {
+namespace FLEXATTN_TU_NAMESPACE {
 
 constexpr int kThreads = 320;  // warps 0-3, 4-7: element-wise warpgroups (64 query columns each); 8: MMA; 9: TMA
 constexpr int kMmaWarp = 8, kTmaWarp = 9;
@@ -54,12 +54,22 @@ __device__ __forceinline__ void load_stats32(float (&dst)[32], const float* __re
 // First element-wise phase, 32 columns: this thread's key row against query columns i_first .. i_first+31.
 // s: raw S^T values in, p * dsigma (the factor dS^T needs) out; pk_p: packed bf16 P^T.  The mask functor is
 // compiled in only for partial tiles.
-template <int SK, int MK, bool kPartial>
+// what a user score function sees besides the score and the positions
+struct ScoreCtx {
+  float sm_scale;
+  int b, h;
+};
+
+// kBias: ab_col points at the dense bias element (query i_first, key j) of this thread's key (nullptr: none, or a
+// key past the end); consecutive queries are ab_stride floats apart, so a warp (32 consecutive keys) reads 128
+// contiguous bytes per query.
+template <int SK, int MK, bool kPartial, bool kBias = false>
 __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __restrict__ pk_p, const float (&nl)[32],
                                              const int32_t* __restrict__ s_doc, int i_first, int j, int dj, int seq_q,
                                              int window, int stride, float c2, float slope2, float abase, float capl2,
-                                             float csc) {
-  if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+                                             float csc, const ScoreCtx ctx, const float* __restrict__ ab_col = nullptr,
+                                             size_t ab_stride = 0) {
+  if constexpr (SK == FLEXATTN_SCORE_SOFTCAP || SK == FLEXATTN_SCORE_USER) {
     // scalar form: the packed one costs registers here (tanh, its derivative and the mask live together)
 #pragma unroll
     for (int c = 0; c < 32; c += 2) {
@@ -67,15 +77,27 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int cc = c + u;
-        const float th = ptx::tanh_approx(__uint_as_float(s[cc]) * csc);
-        float p = ptx::ex2(fmaf(capl2, th, nl[cc]));
+        float arg, dsig;  // log2-domain logit minus the row's log-sum-exp; derivative of the score function
+        if constexpr (SK == FLEXATTN_SCORE_USER) {
+          const float sc = __uint_as_float(s[cc]) * ctx.sm_scale;
+          arg = fmaf(user_score(sc, ctx.b, ctx.h, i_first + cc, j), kLog2e, nl[cc]);
+          dsig = user_dscore(sc, ctx.b, ctx.h, i_first + cc, j);
+        } else {
+          const float th = ptx::tanh_approx(__uint_as_float(s[cc]) * csc);
+          arg = fmaf(capl2, th, nl[cc]);
+          dsig = fmaf(-th, th, 1.f);
+        }
+        if constexpr (kBias) {
+          if (ab_col != nullptr && i_first + cc < seq_q) arg = fmaf(__ldg(ab_col + (size_t)cc * ab_stride), kLog2e, arg);
+        }
+        float p = ptx::ex2(arg);
         if constexpr (kPartial) {
           const int i = i_first + cc;
           const int di = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[cc] : 0;
           p = ((i < seq_q) && mask_keep<MK>(i, j, window, stride, di, dj)) ? p : 0.f;
         }
         pv[u] = p;
-        s[cc] = __float_as_uint(p * fmaf(-th, th, 1.f));
+        s[cc] = __float_as_uint(p * dsig);
       }
       pk_p[c >> 1] = ptx::pack_bf16_trunc(pv[0], pv[1]);
     }
@@ -87,22 +109,22 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
   for (int c = 0; c < 32; c += 2) {
     const uint64_t sv2 = ptx::pack2(__uint_as_float(s[c]), __uint_as_float(s[c + 1]));
     const uint64_t nl2 = ptx::pack2(nl[c], nl[c + 1]);
-    uint64_t arg2, dsig2 = 0;  // arg = log2-domain logit minus the row's log-sum-exp
+    uint64_t arg2;  // arg = log2-domain logit minus the row's log-sum-exp
     if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
       // bias = abase - slope2 * column: the column part is a compile-time pair
       const uint64_t b2 = ptx::fma2(ptx::pack2(-(float)c, -(float)(c + 1)), ptx::pack2(slope2, slope2), ptx::pack2(abase, abase));
       arg2 = ptx::fma2(sv2, c22, ptx::add2(b2, nl2));
-    } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
-      float t0, t1;
-      ptx::unpack2(ptx::mul2(sv2, ptx::pack2(csc, csc)), t0, t1);
-      const uint64_t th2 = ptx::pack2(ptx::tanh_approx(t0), ptx::tanh_approx(t1));
-      arg2 = ptx::fma2(ptx::pack2(capl2, capl2), th2, nl2);
-      dsig2 = ptx::fma2(ptx::sub2(0ull, th2), th2, ptx::pack2(1.f, 1.f));
     } else {
       arg2 = ptx::fma2(sv2, c22, nl2);
     }
     float a0, a1;
     ptx::unpack2(arg2, a0, a1);
+    if constexpr (kBias) {
+      if (ab_col != nullptr) {
+        if (i_first + c < seq_q) a0 = fmaf(__ldg(ab_col + (size_t)c * ab_stride), kLog2e, a0);
+        if (i_first + c + 1 < seq_q) a1 = fmaf(__ldg(ab_col + (size_t)(c + 1) * ab_stride), kLog2e, a1);
+      }
+    }
     float p0 = ptx::ex2(a0), p1 = ptx::ex2(a1);
     if constexpr (kPartial) {
       const int i = i_first + c;
@@ -111,7 +133,6 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
       p1 = ((i + 1 < seq_q) && mask_keep<MK>(i + 1, j, window, stride, d1, dj)) ? p1 : 0.f;
     }
     pk_p[c >> 1] = ptx::pack_bf16_trunc(p0, p1);
-    if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) ptx::unpack2(ptx::mul2(ptx::pack2(p0, p1), dsig2), p0, p1);
     s[c] = __float_as_uint(p0);
     s[c + 1] = __float_as_uint(p1);
   }
@@ -131,7 +152,9 @@ __device__ __forceinline__ void dkv_ds_math32(const uint32_t (&pd)[32], const ui
 }
 
 template <int D, int SK, int MK>
-__global__ void __launch_bounds__(kThreads, 1)
+// 192 registers per thread: 10 warps x 6144 registers (a warp's registers are allocated in units of 512) fill the
+// register file.  __launch_bounds__(320) alone caps the kernel at 168 and makes the element-wise loops spill.
+__global__ void __maxnreg__(192)
     dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                      const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
@@ -319,6 +342,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const float csc = (SK == FLEXATTN_SCORE_SOFTCAP) ? P.sm_scale / P.cap : 0.f;
     const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
     const int dj = (MK == FLEXATTN_MASK_DOCUMENT && row_ok) ? doc[j] : -2;
+    const ScoreCtx ctx{P.sm_scale, b, h};
     bool ok = true;
     int fail_at = 0;
 
@@ -379,7 +403,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int n = 0; n < N; ++n) {
       const int st = n & 1;
       const int qt = cm.x + n, i0 = qt * kTile + 64 * half;  // first query position of this warpgroup's columns
-      const bool partial = !(qt >= cm.z && qt < cm.w);
+      const bool partial = P.ab != nullptr || !(qt >= cm.z && qt < cm.w);  // with a dense bias: always the masked form
       // the statistics of this tile were staged during the previous tile (or before the loop)
       // a failed wait never leaves the loop early: every thread keeps executing the same named barriers
       ptx::cp_async_wait_all();  // this thread's asynchronous copies for this tile have landed
@@ -400,16 +424,24 @@ __global__ void __launch_bounds__(kThreads, 1)
       {
         uint32_t pk_p[32];
         const float abase = slope2 * (float)(j - i0);  // ALiBi bias = slope * (j - i), i = i0 + column
-        if (partial) {
+        if (P.ab != nullptr) {
+          // element (query i0, key j) of the dense bias; nullptr for a key past the end of the sequence
+          const float* ab_col = row_ok ? P.ab + ((size_t)bh * P.seq_q + i0) * P.seq_k + j : nullptr;
+          dkv_p_math32<SK, MK, true, true>(sr[0], pk_p, st0, &sh->doc[st][64 * half], i0, j, dj, P.seq_q, P.window,
+                                           P.stride, c2, slope2, abase, capl2, csc, ctx, ab_col, (size_t)P.seq_k);
+          dkv_p_math32<SK, MK, true, true>(sr[1], pk_p + 16, st1, &sh->doc[st][64 * half + 32], i0 + 32, j, dj, P.seq_q,
+                                           P.window, P.stride, c2, slope2, abase - 32.f * slope2, capl2, csc, ctx,
+                                           ab_col != nullptr ? ab_col + 32 * (size_t)P.seq_k : nullptr, (size_t)P.seq_k);
+        } else if (partial) {
           dkv_p_math32<SK, MK, true>(sr[0], pk_p, st0, &sh->doc[st][64 * half], i0, j, dj, P.seq_q, P.window,
-                                     P.stride, c2, slope2, abase, capl2, csc);
+                                     P.stride, c2, slope2, abase, capl2, csc, ctx);
           dkv_p_math32<SK, MK, true>(sr[1], pk_p + 16, st1, &sh->doc[st][64 * half + 32], i0 + 32, j, dj, P.seq_q,
-                                     P.window, P.stride, c2, slope2, abase - 32.f * slope2, capl2, csc);
+                                     P.window, P.stride, c2, slope2, abase - 32.f * slope2, capl2, csc, ctx);
         } else {
           dkv_p_math32<SK, MK, false>(sr[0], pk_p, st0, &sh->doc[st][64 * half], i0, j, dj, P.seq_q, P.window,
-                                      P.stride, c2, slope2, abase, capl2, csc);
+                                      P.stride, c2, slope2, abase, capl2, csc, ctx);
           dkv_p_math32<SK, MK, false>(sr[1], pk_p + 16, st1, &sh->doc[st][64 * half + 32], i0 + 32, j, dj, P.seq_q,
-                                      P.window, P.stride, c2, slope2, abase - 32.f * slope2, capl2, csc);
+                                      P.window, P.stride, c2, slope2, abase - 32.f * slope2, capl2, csc, ctx);
         }
         ptx::tmem_st32(lane_base + colS, pk_p);  // bf16 P^T over the first half of this warpgroup's S^T columns
         ptx::tmem_wait_st();
@@ -502,6 +534,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+#ifndef FLEXATTN_JIT
 template <int D, int SK, int MK>
 int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const CUtensorMap& tdo,
                const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdk, const CUtensorMap& tdv,
@@ -543,8 +576,11 @@ int launch_score(cudaStream_t st, const DevParams& d, int score, int mask, const
   }
 }
 
-}  // namespace
+#endif  // !FLEXATTN_JIT
 
+}  // namespace FLEXATTN_TU_NAMESPACE
+
+#ifndef FLEXATTN_JIT
 int launch_sm100_dkv(cudaStream_t st, const DevParams& d, int score, int mask) {
   int* af = abort_flag_ptr();
   if (af == nullptr) return FLEXATTN_ERR_CUDA;
@@ -562,9 +598,17 @@ int launch_sm100_dkv(cudaStream_t st, const DevParams& d, int score, int mask) {
   if (e) return e;
   e = make_tile_map(&tdv, d.dv, slices, d.seq_k, d.head_dim);
   if (e) return e;
+  if (score == FLEXATTN_SCORE_USER) {
+    // a kernel compiled at run time around the registered score function: same parameters, grid and shared memory
+    const size_t need = 6 * (size_t)(d.head_dim / 64) * ptx::kPanelBytes + sizeof(DkvSmem) + 1024;
+    void* args[] = {&tq, &tdo, &tk, &tv, &tdk, &tdv, const_cast<DevParams*>(&d), &af};
+    return jit_launch(2, d.user_score, d.head_dim, mask, (unsigned)d.n_kt, (unsigned)(d.batch * d.heads), kThreads,
+                      need > 120 * 1024 ? need : 120 * 1024, st, args);
+  }
   if (d.head_dim == 128) return launch_score<128>(st, d, score, mask, tq, tdo, tk, tv, tdk, tdv, af);
   if (d.head_dim == 64) return launch_score<64>(st, d, score, mask, tq, tdo, tk, tv, tdk, tdv, af);
   return FLEXATTN_ERR_UNSUPPORTED_HEAD_DIM;
 }
+#endif  // !FLEXATTN_JIT
 
 }  // namespace flexattn

@@ -27,7 +27,7 @@
 
 
 namespace flexattn {
-namespace {
+namespace FLEXATTN_TU_NAMESPACE {
 
 constexpr int kThreads = 320;  // warps 0-3, 4-7: element-wise warpgroups (64 key columns each); 8: MMA; 9: TMA
 constexpr int kMmaWarp = 8, kTmaWarp = 9;
@@ -48,14 +48,24 @@ struct DqSmem {
 // This thread's 64 columns (keys j_first .. j_first+63) of its query row: raw S and dP in, packed bf16 dS out.
 // nlse2 = log2(1 + 2^-9) - (m log2e + log2 l) (pre-scaling for pack_bf16_trunc) and delta belong to the row.  The mask functor is compiled in only for partial
 // tiles.
-template <int SK, int MK, bool kPartial>
+// what a user score function sees besides the score and the positions
+struct ScoreCtx {
+  float sm_scale;
+  int b, h;
+};
+
+template <int SK, int MK, bool kPartial, bool kBias = false>
 __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const uint32_t (&pr)[2][32],
                                              uint32_t (&pk)[32], float nlse2, float delta,
                                              const int32_t* __restrict__ s_doc, int i, int di, int j_first, int seq_k,
                                              int window, int stride, float c2, float slope2, float abase, float capl2,
-                                             float csc) {
+                                             float csc, const ScoreCtx ctx, const float* __restrict__ ab_row = nullptr,
+                                             float* __restrict__ dab_row = nullptr) {
   const float bias0 = abase + nlse2;  // ALiBi: slope * (j_first - i), folded with the row's -lse2
-  if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+  // kBias: ab_row / dab_row point at this row's element of column j_first (nullptr: none, or a row past the end);
+  // the bias joins the logit after the score function, and its gradient is p * (dp - delta) before sigma'.
+  float bias[8];
+  if constexpr (SK == FLEXATTN_SCORE_SOFTCAP || SK == FLEXATTN_SCORE_USER) {
     // scalar form: the packed one costs registers here (tanh, its derivative and the mask live together)
 #pragma unroll
     for (int c = 0; c < 64; c += 2) {
@@ -63,14 +73,37 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int cc = c + u;
-        const float th = ptx::tanh_approx(__uint_as_float(sr[cc >> 5][cc & 31]) * csc);
-        float p = ptx::ex2(fmaf(capl2, th, nlse2));
+        float arg, dsig;  // log2-domain logit minus the row's log-sum-exp; derivative of the score function
+        if constexpr (SK == FLEXATTN_SCORE_USER) {
+          const float sc = __uint_as_float(sr[cc >> 5][cc & 31]) * ctx.sm_scale;
+          arg = fmaf(user_score(sc, ctx.b, ctx.h, i, j_first + cc), kLog2e, nlse2);
+          dsig = user_dscore(sc, ctx.b, ctx.h, i, j_first + cc);
+        } else {
+          const float th = ptx::tanh_approx(__uint_as_float(sr[cc >> 5][cc & 31]) * csc);
+          arg = fmaf(capl2, th, nlse2);
+          dsig = fmaf(-th, th, 1.f);
+        }
+        if constexpr (kBias) {
+          if ((cc & 7) == 0) {
+            if (ab_row != nullptr) ptx::load_bias8(bias, ab_row + cc, seq_k - (j_first + cc));
+            else
+#pragma unroll
+              for (int w = 0; w < 8; ++w) bias[w] = 0.f;
+          }
+          arg = fmaf(bias[cc & 7], kLog2e, arg);
+        }
+        float p = ptx::ex2(arg);
         if constexpr (kPartial) {
           const int j = j_first + cc;
           const int dj = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[cc] : 0;
           p = ((j < seq_k) && mask_keep<MK>(i, j, window, stride, di, dj)) ? p : 0.f;
         }
-        dv[u] = p * (__uint_as_float(pr[cc >> 5][cc & 31]) - delta) * fmaf(-th, th, 1.f);
+        const float dt = p * (__uint_as_float(pr[cc >> 5][cc & 31]) - delta);
+        if constexpr (kBias) {
+          // p carries the (1 + 2^-9) pre-scaling meant for the truncating bf16 pack: undo it for the f32 gradient
+          if (dab_row != nullptr && j_first + cc < seq_k) dab_row[cc] = dt * ptx::kRoundInv;
+        }
+        dv[u] = dt * dsig;
       }
       pk[c >> 1] = ptx::pack_bf16_trunc(dv[0], dv[1]);
     }
@@ -82,21 +115,25 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
   for (int c = 0; c < 64; c += 2) {
     const uint64_t s2 = ptx::pack2(__uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1]));
     const uint64_t dp2 = ptx::pack2(__uint_as_float(pr[c >> 5][c & 31]), __uint_as_float(pr[c >> 5][(c & 31) + 1]));
-    uint64_t arg2, dsig2 = 0;
+    uint64_t arg2;
     if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
       const uint64_t b2 = ptx::fma2(ptx::pack2((float)c, (float)(c + 1)), ptx::pack2(slope2, slope2), ptx::pack2(bias0, bias0));
       arg2 = ptx::fma2(s2, c22, b2);
-    } else if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
-      float t0, t1;
-      ptx::unpack2(ptx::mul2(s2, ptx::pack2(csc, csc)), t0, t1);
-      const uint64_t th2 = ptx::pack2(ptx::tanh_approx(t0), ptx::tanh_approx(t1));
-      arg2 = ptx::fma2(ptx::pack2(capl2, capl2), th2, nl2);
-      dsig2 = ptx::fma2(ptx::sub2(0ull, th2), th2, ptx::pack2(1.f, 1.f));
     } else {
       arg2 = ptx::fma2(s2, c22, nl2);
     }
     float a0, a1;
     ptx::unpack2(arg2, a0, a1);
+    if constexpr (kBias) {
+      if ((c & 7) == 0) {
+        if (ab_row != nullptr) ptx::load_bias8(bias, ab_row + c, seq_k - (j_first + c));
+        else
+#pragma unroll
+          for (int w = 0; w < 8; ++w) bias[w] = 0.f;
+      }
+      a0 = fmaf(bias[c & 7], kLog2e, a0);
+      a1 = fmaf(bias[(c & 7) + 1], kLog2e, a1);
+    }
     float p0 = ptx::ex2(a0), p1 = ptx::ex2(a1);
     if constexpr (kPartial) {
       const int j = j_first + c;
@@ -104,16 +141,23 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
       p0 = ((j < seq_k) && mask_keep<MK>(i, j, window, stride, di, d0)) ? p0 : 0.f;
       p1 = ((j + 1 < seq_k) && mask_keep<MK>(i, j + 1, window, stride, di, d1)) ? p1 : 0.f;
     }
-    uint64_t d2 = ptx::mul2(ptx::pack2(p0, p1), ptx::sub2(dp2, dl2));
-    if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) d2 = ptx::mul2(d2, dsig2);
+    const uint64_t d2 = ptx::mul2(ptx::pack2(p0, p1), ptx::sub2(dp2, dl2));
     float d0f, d1f;
     ptx::unpack2(d2, d0f, d1f);
+    if constexpr (kBias) {
+      if (dab_row != nullptr) {  // f32 gradient of the bias: undo the pre-scaling meant for the truncating bf16 pack
+        if (j_first + c < seq_k) dab_row[c] = d0f * ptx::kRoundInv;
+        if (j_first + c + 1 < seq_k) dab_row[c + 1] = d1f * ptx::kRoundInv;
+      }
+    }
     pk[c >> 1] = ptx::pack_bf16_trunc(d0f, d1f);
   }
 }
 
 template <int D, int SK, int MK>
-__global__ void __launch_bounds__(kThreads, 1)
+// 192 registers per thread: 10 warps x 6144 registers (a warp's registers are allocated in units of 512) fill the
+// register file.  __launch_bounds__(320) alone caps the kernel at 168 and makes the element-wise loops spill.
+__global__ void __maxnreg__(192)
     dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const __grid_constant__ CUtensorMap tm_dq, const DevParams P, int* abort_flag) {
@@ -358,6 +402,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::mbar_arrive_warp(&sh->bar_qtm);
     };
     bool copied_ahead = false;  // this item's Q, dO were already copied during the previous item's last tile
+    const bool has_bias = P.ab != nullptr || P.dab != nullptr;  // dense bias and / or its gradient requested
 
     for (int r = 0; r * G + ((r & 1) ? G - 1 - cta : cta) < total; ++r) {
       // the Q/dO entry of the item has landed, and with it the item's descriptor
@@ -382,6 +427,23 @@ __global__ void __launch_bounds__(kThreads, 1)
       // l == 0 (fully masked row): force p to 0; kRoundLog2 pre-scales p (and so dS) for pack_bf16_trunc
       const float nlse2 = row_ok ? (l_ > 0.f ? ptx::kRoundLog2 - fmaf(m_, kLog2e, log2f(l_)) : -1.0e30f) : ptx::kRoundLog2;
 
+      // dense bias / its gradient: this query row's first element (nullptr: none, or a row past the end)
+      const ScoreCtx ctx{P.sm_scale, b, h};
+      const float* ab_q = (P.ab != nullptr && row_ok) ? P.ab + ((size_t)bh * P.seq_q + i) * P.seq_k : nullptr;
+      float* dab_q = (P.dab != nullptr && row_ok) ? P.dab + ((size_t)bh * P.seq_q + i) * P.seq_k : nullptr;
+      if (P.dab != nullptr) {
+        // the bias gradient is dense: the columns of kv tiles this item never visits get their zeros here
+        // (warp = row, lanes along the row: coalesced)
+        const int kbeg = min(rm.x * kTile, P.seq_k), kend = min(rm.y * kTile, P.seq_k);
+        for (int r = warp; r < kTile; r += 8) {
+          const int ir = qt * kTile + r;
+          if (ir >= P.seq_q) break;
+          float* zrow = P.dab + ((size_t)bh * P.seq_q + ir) * P.seq_k;
+          for (int j = lane; j < kbeg; j += 32) zrow[j] = 0.f;
+          for (int j = kend + lane; j < P.seq_k; j += 32) zrow[j] = 0.f;
+        }
+      }
+
       if (ok && !copied_ahead) copy_q_do(e);
       copied_ahead = false;
       ++e;
@@ -389,7 +451,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
       for (int n = 0; n < N; ++n, ++T, ++e) {
         const int kt = rm.x + n, j0 = kt * kTile + 64 * half;  // first key position of this thread's columns
-        const bool partial = !(kt >= rm.z && kt < rm.w);
+        const bool partial = has_bias || !(kt >= rm.z && kt < rm.w);  // with a bias: always the masked form
         if (MK == FLEXATTN_MASK_DOCUMENT && partial) {
           if (row < 64) {
             const int j = j0 + row;
@@ -429,12 +491,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::mbar_arrive_warp(&sh->bar_ld);  // S / dP columns may be overwritten by the next tile's MMAs
         uint32_t pk[32];
         const float abase = slope2 * (float)(j0 - i);
-        if (partial)
+        if (has_bias)
+          dq_half_math<SK, MK, true, true>(sr, pr, pk, nlse2, delta, &sh->doc[T & 1][64 * half], i, di, j0, P.seq_k,
+                                           P.window, P.stride, c2, slope2, abase, capl2, csc, ctx,
+                                           ab_q != nullptr ? ab_q + j0 : nullptr, dab_q != nullptr ? dab_q + j0 : nullptr);
+        else if (partial)
           dq_half_math<SK, MK, true>(sr, pr, pk, nlse2, delta, &sh->doc[T & 1][64 * half], i, di, j0, P.seq_k, P.window,
-                                     P.stride, c2, slope2, abase, capl2, csc);
+                                     P.stride, c2, slope2, abase, capl2, csc, ctx);
         else
           dq_half_math<SK, MK, false>(sr, pr, pk, nlse2, delta, &sh->doc[T & 1][64 * half], i, di, j0, P.seq_k, P.window,
-                                      P.stride, c2, slope2, abase, capl2, csc);
+                                      P.stride, c2, slope2, abase, capl2, csc, ctx);
         if (n > 0) {  // the dQ MMA of the previous tile must have read the dS buffer
           ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dq, (T - 1) & 1));
           if (!ok) { fail_at = 11; continue; }
@@ -504,6 +570,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+#ifndef FLEXATTN_JIT
 template <int D, int SK, int MK>
 int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const CUtensorMap& tdo,
                const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdq, int* abort_flag) {
@@ -548,8 +615,11 @@ int launch_score(cudaStream_t st, const DevParams& d, int score, int mask, const
   }
 }
 
-}  // namespace
+#endif  // !FLEXATTN_JIT
 
+}  // namespace FLEXATTN_TU_NAMESPACE
+
+#ifndef FLEXATTN_JIT
 int launch_sm100_dq(cudaStream_t st, const DevParams& d, int score, int mask) {
   int* af = abort_flag_ptr();
   if (af == nullptr) return FLEXATTN_ERR_CUDA;
@@ -565,9 +635,20 @@ int launch_sm100_dq(cudaStream_t st, const DevParams& d, int score, int mask) {
   if (e) return e;
   e = make_tile_map(&tdq, d.dq, slices, d.seq_q, d.head_dim);
   if (e) return e;
+  if (score == FLEXATTN_SCORE_USER) {
+    // a kernel compiled at run time around the registered score function: same parameters, grid and shared memory
+    const size_t need = 6 * (size_t)(d.head_dim / 64) * ptx::kPanelBytes + 2 * ptx::kPanelBytes + sizeof(DqSmem) + 1024;
+    const long long items = (long long)d.n_qt * d.batch * d.heads;
+    const int sms = sm_count();
+    if (sms <= 0) return FLEXATTN_ERR_CUDA;
+    void* args[] = {&tq, &tdo, &tk, &tv, &tdq, const_cast<DevParams*>(&d), &af};
+    return jit_launch(1, d.user_score, d.head_dim, mask, (unsigned)(items < sms ? items : sms), 1, kThreads,
+                      need > 120 * 1024 ? need : 120 * 1024, st, args);
+  }
   if (d.head_dim == 128) return launch_score<128>(st, d, score, mask, tq, tdo, tk, tv, tdq, af);
   if (d.head_dim == 64) return launch_score<64>(st, d, score, mask, tq, tdo, tk, tv, tdq, af);
   return FLEXATTN_ERR_UNSUPPORTED_HEAD_DIM;
 }
+#endif  // !FLEXATTN_JIT
 
 }  // namespace flexattn

@@ -1,8 +1,25 @@
 // Internal definitions shared by every translation unit of libflexattn.so.
 #pragma once
+#ifdef FLEXATTN_JIT
+// Run-time compilation (NVRTC) of a tensor-core kernel around a user score function: no host headers exist there,
+// so the handful of types the device code needs are spelled out.
+typedef signed char int8_t;
+typedef unsigned char uint8_t;
+typedef unsigned short uint16_t;
+typedef int int32_t;
+typedef unsigned int uint32_t;
+typedef long long int64_t;
+typedef unsigned long long uint64_t;
+typedef unsigned long long uintptr_t;
+struct alignas(64) CUtensorMap_st {
+  unsigned long long opaque[16];
+};
+typedef CUtensorMap_st CUtensorMap;
+#else
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#endif
 
 #include "../../include/flexattn.h"
 
@@ -78,6 +95,7 @@ struct DevParams {
   int n_qt, n_kt, map_rows, doc_stride;
   int window, stride;
   float sm_scale, cap;
+  int user_score;  // handle of a run-time compiled score function (host side only)
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -133,6 +151,7 @@ __device__ __forceinline__ void report_timeout(int32_t* status, int kernel_id, i
   }
 }
 
+#ifndef FLEXATTN_JIT
 // Host-side validation of a forward call, shared by flexattn_fwd and flexattn_fwd_noalloc (api.cu).
 int validate_fwd_args(const FlexAttnParams* p, bool* tc);
 
@@ -149,4 +168,14 @@ int launch_sm100_fwd_pipe(cudaStream_t st, const DevParams& d, int score, int ma
 int launch_sm100_dq(cudaStream_t st, const DevParams& d, int score, int mask);
 int launch_sm100_dkv(cudaStream_t st, const DevParams& d, int score, int mask);
 
+// Launch of a kernel compiled at run time around a user score function (jit.cu).  which: 0 forward, 1 dQ, 2 dK/dV;
+// args: the kernel's parameters as for cuLaunchKernel.  Returns a FlexAttnStatus.
+int jit_launch(int which, int handle, int head_dim, int mask, unsigned grid_x, unsigned grid_y, unsigned threads,
+               size_t smem_bytes, cudaStream_t st, void** args);
+#endif  // !FLEXATTN_JIT
+
 }  // namespace flexattn
+
+// user_score(s, b, h, i, j) and user_dscore(...): identity here; a run-time compilation substitutes the user's
+// expressions for this header.
+#include "user_score.cuh"

@@ -28,7 +28,7 @@
 #include "sm100.cuh"
 
 namespace flexattn {
-namespace {
+namespace FLEXATTN_TU_NAMESPACE {
 
 constexpr int kThreads = 352;
 constexpr int kMmaWarp = 8, kTmaWarp = 9, kTmaWarpV = 10;
@@ -46,18 +46,38 @@ struct PipeSmem {
 };
 
 // x: this thread's 64 raw scores (columns c_base .. c_base+63 of the tile) -> log2-domain logits in place;
-// returns their maximum.
-template <int SK, int MK, bool kPartial>
+// returns their maximum.  kBias: ab_row points at the bias of this row's first column (nullptr for a row past the
+// end of the sequence); the bias is added after the score function and before the mask.
+// what a user score function sees besides the score and the positions
+struct ScoreCtx {
+  float sm_scale;
+  int b, h;
+};
+
+template <int SK, int MK, bool kPartial, bool kBias = false>
 __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, int c_base, int seq_k, int window,
                                             int stride, float c2, float slope2, float capl2, float csc, int di,
-                                            const int32_t* s_doc) {
+                                            const int32_t* s_doc, const ScoreCtx ctx,
+                                            const float* __restrict__ ab_row = nullptr) {
   float mx[4] = {kMasked, kMasked, kMasked, kMasked};
   const float abase = slope2 * (float)(j0 + c_base - i);
-  if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+  float bias[8];
+  if constexpr (SK == FLEXATTN_SCORE_SOFTCAP || SK == FLEXATTN_SCORE_USER) {
     // scalar form: the packed one costs registers here
 #pragma unroll
     for (int c = 0; c < kHalf; ++c) {
-      float t = capl2 * ptx::tanh_approx(x[c] * csc);
+      float t;
+      if constexpr (SK == FLEXATTN_SCORE_USER) t = user_score(x[c] * ctx.sm_scale, ctx.b, ctx.h, i, j0 + c_base + c) * kLog2e;
+      else t = capl2 * ptx::tanh_approx(x[c] * csc);
+      if constexpr (kBias) {
+        if ((c & 7) == 0) {
+          if (ab_row != nullptr) ptx::load_bias8(bias, ab_row + c, seq_k - (j0 + c_base + c));
+          else
+#pragma unroll
+            for (int u = 0; u < 8; ++u) bias[u] = 0.f;
+        }
+        t = fmaf(bias[c & 7], kLog2e, t);
+      }
       if constexpr (kPartial) {
         const int j = j0 + c_base + c;
         const int dj = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c_base + c] : 0;
@@ -79,6 +99,16 @@ __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, in
     } else {
       ptx::unpack2(ptx::mul2(x2, ptx::pack2(c2, c2)), t0, t1);
     }
+    if constexpr (kBias) {
+      if ((c & 7) == 0) {
+        if (ab_row != nullptr) ptx::load_bias8(bias, ab_row + c, seq_k - (j0 + c_base + c));
+        else
+#pragma unroll
+          for (int u = 0; u < 8; ++u) bias[u] = 0.f;
+      }
+      t0 = fmaf(bias[c & 7], kLog2e, t0);
+      t1 = fmaf(bias[(c & 7) + 1], kLog2e, t1);
+    }
     if constexpr (kPartial) {
       const int j = j0 + c_base + c;
       const int d0 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c_base + c] : 0;
@@ -95,7 +125,9 @@ __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, in
 }
 
 template <int D, int SK, int MK>
-__global__ void __launch_bounds__(kThreads, 1)
+// 176 registers per thread: 11 warps x 5632 registers (a warp's registers are allocated in units of 512) fill the
+// register file.  __launch_bounds__(352) alone caps the kernel at 168 and makes the element-wise loops spill.
+__global__ void __maxnreg__(176)
     fwd_pipe_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                           const DevParams P, int* abort_flag) {
@@ -315,12 +347,15 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
       const int di = (MK == FLEXATTN_MASK_DOCUMENT && i < P.seq_q) ? doc[i] : 0;
       float m_ref = kMasked, m_true = kMasked, l = 0.f;  // l: sum over this thread's columns only
+      // dense bias of this query row (nullptr: no bias, or a row past the end of the sequence)
+      const float* ab_q = (P.ab != nullptr && i < P.seq_q) ? P.ab + ((size_t)bh * P.seq_q + i) * P.seq_k : nullptr;
+      const ScoreCtx ctx{P.sm_scale, b, h};
 
       for (int n = 0; n < N; ++n, ++T) {
         const uint32_t par = T & 1;
         const uint32_t colS = (uint32_t)sb * 128u;
         const int kt = rm.x + n, j0 = kt * kTile;
-        const bool partial = !(kt >= rm.z && kt < rm.w);
+        const bool partial = P.ab != nullptr || !(kt >= rm.z && kt < rm.w);
         if (MK == FLEXATTN_MASK_DOCUMENT && partial && half == 0) {
           const int j = j0 + row;
           sh->doc[par][row] = (j < P.seq_k) ? doc[j] : -1;
@@ -350,12 +385,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         // scores and folds sm_scale*log2e into the FMA that also subtracts the running max)
         float tmax = kMasked, xs = 1.0f;
         if (ok) {
-          if (partial) {
+          if (P.ab != nullptr) {
+            // with a bias every tile takes the masked form (the mask functor also clips the ragged last tile):
+            // the S^2 floats of the bias bound this path, not the arithmetic
+            tmax = score_half<SK, MK, true, true>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc,
+                                                  di, sh->doc[par], ctx, ab_q != nullptr ? ab_q + j0 + c_base : nullptr);
+          } else if (partial) {
             tmax = score_half<SK, MK, true>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di,
-                                            sh->doc[par]);
+                                            sh->doc[par], ctx);
           } else if constexpr (SK != FLEXATTN_SCORE_NONE) {
             tmax = score_half<SK, MK, false>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di,
-                                             sh->doc[par]);
+                                             sh->doc[par], ctx);
           } else {
             float mx[4] = {x[0], x[1], x[2], x[3]};
 #pragma unroll
@@ -478,7 +518,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           o_pending = true;
         }
       } else if (ok && i < P.seq_q) {  // an item without any kv tile: zeros, written directly
-        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(P.o) + grow * D;
+        uint16_t* orow = static_cast<uint16_t*>(P.o) + grow * D;   // bf16 elements
         for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 8)
           *reinterpret_cast<uint4*>(orow + c0) = make_uint4(0u, 0u, 0u, 0u);
       }
@@ -500,6 +540,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+#ifndef FLEXATTN_JIT
 template <int D, int SK, int MK>
 int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const CUtensorMap& tk,
                const CUtensorMap& tv, const CUtensorMap& to, int* abort_flag) {
@@ -544,8 +585,11 @@ int launch_score(cudaStream_t st, const DevParams& d, int score, int mask, const
   }
 }
 
-}  // namespace
+#endif  // !FLEXATTN_JIT
 
+}  // namespace FLEXATTN_TU_NAMESPACE
+
+#ifndef FLEXATTN_JIT
 int launch_sm100_fwd_pipe(cudaStream_t st, const DevParams& d, int score, int mask) {
   int* af = abort_flag_ptr();
   if (af == nullptr) return FLEXATTN_ERR_CUDA;
@@ -559,9 +603,20 @@ int launch_sm100_fwd_pipe(cudaStream_t st, const DevParams& d, int score, int ma
   if (e) return e;
   e = make_tile_map(&to, d.o, slices, d.seq_q, d.head_dim);
   if (e) return e;
+  if (score == FLEXATTN_SCORE_USER) {
+    // a kernel compiled at run time around the registered score function: same parameters, grid and shared memory
+    const size_t need = 6 * (size_t)(d.head_dim / 64) * ptx::kPanelBytes + sizeof(PipeSmem) + 1024;
+    const long long items = (long long)d.n_qt * d.batch * d.heads;
+    const int sms = sm_count();
+    if (sms <= 0) return FLEXATTN_ERR_CUDA;
+    void* args[] = {&tq, &tk, &tv, &to, const_cast<DevParams*>(&d), &af};
+    return jit_launch(0, d.user_score, d.head_dim, mask, (unsigned)(items < sms ? items : sms), 1, kThreads,
+                      need > 120 * 1024 ? need : 120 * 1024, st, args);
+  }
   if (d.head_dim == 128) return launch_score<128>(st, d, score, mask, tq, tk, tv, to, af);
   if (d.head_dim == 64) return launch_score<64>(st, d, score, mask, tq, tk, tv, to, af);
   return FLEXATTN_ERR_UNSUPPORTED_HEAD_DIM;
 }
+#endif  // !FLEXATTN_JIT
 
 }  // namespace flexattn

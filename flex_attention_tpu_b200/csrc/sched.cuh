@@ -67,6 +67,7 @@ struct ItemCursor {
   }
 };
 
+#ifndef FLEXATTN_JIT
 // Number of SMs of the current device (queried once per device); -1 on error.
 inline int sm_count() {
   static int cached[64] = {0};
@@ -79,5 +80,6 @@ inline int sm_count() {
   }
   return cached[dev];
 }
+#endif  // !FLEXATTN_JIT
 
 }  // namespace flexattn

@@ -2,7 +2,9 @@
 // tcgen05 (tensor memory allocation, MMA, commit, ld/st, fences) and the shared-memory / instruction
 // descriptors the MMAs consume.  Every wait is bounded: it gives up after kWaitLimitNs and reports.
 #pragma once
+#ifndef FLEXATTN_JIT
 #include <cuda.h>
+#endif
 
 #include "common.cuh"
 
@@ -365,6 +367,19 @@ __device__ __forceinline__ float tanh_approx(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Eight consecutive values of a dense bias row (zeros past the first `n`): two 16-byte loads when the row start
+// allows it, scalar loads otherwise.  The dense additive bias (the reference's `ab`, flex_attention_kernel.py:262-266)
+// is read straight from global memory: with a bias the kernels are bound by those S^2 floats, not by the math.
+__device__ __forceinline__ void load_bias8(float (&b)[8], const float* __restrict__ p, int n) {
+  if (n >= 8 && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+    const float4 lo = __ldg(reinterpret_cast<const float4*>(p)), hi = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    b[0] = lo.x; b[1] = lo.y; b[2] = lo.z; b[3] = lo.w;
+    b[4] = hi.x; b[5] = hi.y; b[6] = hi.z; b[7] = hi.w;
+  } else {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) b[c] = c < n ? __ldg(p + c) : 0.f;
+  }
+}
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
@@ -376,7 +391,9 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 // it; a CTA that leaves on entry because of it reports {TIMEOUT, kernel id, block, kAbortedOnEntry} in the
 // caller's status words, so a launch that did no work never looks like a success.  nullptr if the address
 // cannot be resolved.
+#ifndef FLEXATTN_JIT
 int* abort_flag_ptr();
+#endif
 constexpr int kAbortedOnEntry = 99;
 
 __device__ __forceinline__ void give_up(int* abort_flag, int32_t* status, int kernel_id, int detail) {
@@ -390,6 +407,7 @@ __device__ __forceinline__ bool aborted_on_entry(const int* abort_flag, int32_t*
   return true;
 }
 
+#ifndef FLEXATTN_JIT
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the CURRENT device only, so "already done" is kept
 // per device (one flag array per kernel instantiation, owned by its launcher).  Returns FLEXATTN_OK or
 // FLEXATTN_ERR_CUDA.
@@ -402,5 +420,14 @@ int ensure_dynamic_smem(const void* kernel, int bytes, SmemAttrOnce* once);
 // Host side: 3-D tensor map over a [slices, rows, cols] bf16 array, box = {64 cols, 128 rows, 1 slice},
 // 128-byte swizzle, out-of-range rows read as zero.
 int make_tile_map(CUtensorMap* out, const void* base, int slices, int rows, int cols);
+#endif  // !FLEXATTN_JIT
+
+// Kernels live in an unnamed namespace in ahead-of-time builds and in a named one when compiled at run time
+// (so that the run-time compiler can be asked for one instantiation by name).
+#ifdef FLEXATTN_JIT
+#define FLEXATTN_TU_NAMESPACE jit_tu
+#else
+#define FLEXATTN_TU_NAMESPACE
+#endif
 
 }  // namespace flexattn

@@ -59,7 +59,7 @@ def flex_attention(q, k, v, ab=None, segment_ids=None, *, causal: bool = False, 
     ``segment_ids``: ``[B, S]`` int32 document ids (selects the document mask when no ``mask_fns`` are given,
     as ``causal`` selects the causal one).  ``block_sizes`` / ``debug`` are accepted and ignored (tile sizes are
     fixed inside the kernels).  ``ab``: optional dense additive bias ``[B, H, Sq, Sk]`` (float32), added to
-    the logits after the score function; it is served by the fp32 SIMT backend and receives a gradient.  The same
+    the logits after the score function; it receives a gradient.  The same
     shape checks as the reference raise ``ValueError`` (``jax_exp.py:156-196``).
     """
     del block_sizes, debug

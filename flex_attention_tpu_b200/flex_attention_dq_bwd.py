@@ -19,7 +19,7 @@ def flex_attention_bwd_dq(q, k, v, ab, segment_ids, l, m, o, do, d, *, block_b=N
                           return_dab=False):
     """dq = sm_scale * (p * (do v^T - d) * score_mod'(s)) k, with p rebuilt from (l, m).
 
-    ``ab``: optional dense additive bias [B, H, Sq, Sk] (float32; served by the SIMT backend).  With
+    ``ab``: optional dense additive bias [B, H, Sq, Sk] (float32).  With
     ``return_dab`` the call returns ``(dq, dab)``, dab = p * (do v^T - d), the gradient of ``ab``
     ("dab is just ds", reference ``jax_exp.py:1676-1677``).
 

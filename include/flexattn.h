@@ -28,14 +28,16 @@
 #ifndef FLEXATTN_H_
 #define FLEXATTN_H_
 
+#ifndef FLEXATTN_JIT /* run-time compilation of the kernels brings its own fixed-width types */
 #include <stddef.h>
 #include <stdint.h>
+#endif
 
 #ifdef __cplusplus
 extern "C" {
 #endif
 
-#define FLEXATTN_ABI_VERSION 3
+#define FLEXATTN_ABI_VERSION 4
 #define FLEXATTN_TILE 128 /* q-tile and kv-tile edge used by the mask map and by every kernel */
 
 typedef enum FlexAttnStatus {
@@ -50,7 +52,9 @@ typedef enum FlexAttnStatus {
   FLEXATTN_ERR_CUDA = 8,
   FLEXATTN_ERR_TIMEOUT = 9,
   FLEXATTN_ERR_UNSUPPORTED_BACKEND = 10,
-  FLEXATTN_ERR_NOALLOC_LIMIT = 11
+  FLEXATTN_ERR_NOALLOC_LIMIT = 11,
+  FLEXATTN_ERR_JIT_UNAVAILABLE = 12, /* the run-time compiler (libnvrtc) or the driver's module loader is missing */
+  FLEXATTN_ERR_JIT_COMPILE = 13      /* a user score function did not compile: see flexattn_user_score_log */
 } FlexAttnStatus;
 
 typedef enum FlexAttnDType { FLEXATTN_BF16 = 0, FLEXATTN_F32 = 1 } FlexAttnDType;
@@ -60,7 +64,8 @@ typedef enum FlexAttnDType { FLEXATTN_BF16 = 0, FLEXATTN_F32 = 1 } FlexAttnDType
 typedef enum FlexAttnScoreKind {
   FLEXATTN_SCORE_NONE = 0,
   FLEXATTN_SCORE_ALIBI = 1,
-  FLEXATTN_SCORE_SOFTCAP = 2
+  FLEXATTN_SCORE_SOFTCAP = 2,
+  FLEXATTN_SCORE_USER = 3 /* a score function registered with flexattn_user_score_create (params.user_score) */
 } FlexAttnScoreKind;
 
 /* mask kinds (keep predicate): reference masks.py:3-6 (none), :15-16 (causal, i >= j),
@@ -115,11 +120,11 @@ typedef struct FlexAttnParams {
    * Only the first report lands: zero it to re-arm.  May be NULL. */
   int32_t* status;
   int32_t backend;            /* FlexAttnBackend */
-  int32_t reserved;
+  int32_t user_score;         /* handle from flexattn_user_score_create; SCORE_USER only, else 0 */
   /* optional dense additive bias, float32 [B,H,Sq,Sk], added to the logits after the score function and before
-   * the mask (the reference's `ab`: flex_attention_kernel.py:262-266, mha_reference.py:50-51).  NULL = none.
-   * Served by the SIMT backend only: with a bias, FLEXATTN_BACKEND_AUTO selects it and
-   * FLEXATTN_BACKEND_TCGEN05 fails with FLEXATTN_ERR_UNSUPPORTED_BACKEND. */
+   * the mask (the reference's `ab`: flex_attention_kernel.py:262-266, flash_attention_dkv_bwd.py:261-266,
+   * mha_reference.py:50-51).  NULL = none.  Every backend serves it; the S^2 floats of the bias then bound the
+   * kernels (HBM), not the arithmetic. */
   const float* ab;
   /* optional gradient of the bias, float32 [B,H,Sq,Sk], written by flexattn_bwd_dq when not NULL:
    * dab = p * (dp - delta), zero at masked pairs ("dab is just ds", jax_exp.py:1676-1677). */
@@ -193,6 +198,30 @@ size_t flexattn_noalloc_scratch_bytes(void);
  * `stream`.  Replaces nothing in the reference. */
 int flexattn_read_mask_map(void* stream, const FlexAttnParams* p, int which, int b, int index,
                            int32_t out[4]);
+
+/* User score functions, compiled into the tensor-core kernels at run time.  Replaces `make_jax_score_fn`
+ * (util.py:150-189), which turns a user's Python function into the code the Pallas kernels inline
+ * (flex_attention_kernel.py:248-255), and the jax.vjp of that function inside the backward kernels
+ * (flex_attention_dq_bwd.py:340-345,373-380).
+ *
+ * `score_expr` and `dscore_expr` are CUDA C++ float expressions over `s` (float: the scaled score
+ * sm_scale * <q_i, k_j>), `b`, `h`, `i`, `j` (int: batch, head, query and key position) and the CUDA math
+ * functions: the score function t = f(s, b, h, i, j) and its derivative df/ds.  The call only records them
+ * and returns a handle (> 0) in *handle.  A kernel specialised for the function (and for the head dimension
+ * and mask kind of the problem) is compiled with NVRTC and loaded the first time a forward / dQ / dK,dV call
+ * uses the handle with score_kind = FLEXATTN_SCORE_USER; that first call blocks for the compilation (seconds),
+ * lets the driver allocate the module's code, and must not happen during stream capture.  Later calls launch
+ * the cached kernel.  bf16 inputs with D in {64, 128} only (the tensor-core kernels).
+ * flexattn_user_score_destroy unloads what was compiled for the handle. */
+int flexattn_user_score_create(const char* score_expr, const char* dscore_expr, int32_t* handle);
+int flexattn_user_score_destroy(int32_t handle);
+/* The compiler's log of the most recent failed compilation for `handle` ("" if none).  Valid until the next call
+ * that uses the handle.  Never NULL. */
+const char* flexattn_user_score_log(int32_t handle);
+/* Compiles (without loading or launching: needs no GPU) the kernel `which` (0 forward, 1 dQ, 2 dK/dV) for the
+ * handle, head_dim and mask_kind, exactly as the first launch would.  Returns FLEXATTN_OK, or
+ * FLEXATTN_ERR_JIT_COMPILE / FLEXATTN_ERR_JIT_UNAVAILABLE.  A test and warm-up hook. */
+int flexattn_user_score_compile(int32_t handle, int which, int32_t head_dim, int32_t mask_kind);
 
 /* Clears the calling device's abort word (stream-ordered memset on `stream`), re-enabling the tensor-core
  * kernels after a device-side time-out.  Replaces nothing in the reference. */

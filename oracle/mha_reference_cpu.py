@@ -42,7 +42,7 @@ import numpy as np
 MASK_VALUE = np.float32(-1e9)  # mha_reference.py:62
 
 MASK_KINDS = ("none", "causal", "sliding_window", "sliding_window_causal", "document", "s2")
-SCORE_KINDS = ("none", "alibi", "softcap")
+SCORE_KINDS = ("none", "alibi", "softcap", "user")
 
 
 def keep_mask(kind, q_idx, k_idx, *, window=None, stride=None, doc_q=None, doc_k=None):
@@ -75,7 +75,7 @@ def _kv_limit(kind, q_hi, sk):
 
 
 def _logits_block(qb, k, *, sm_scale, score_kind, cap, slope, q0, mask_kind, window, stride,
-                  doc_q, doc_k, ab_block):
+                  doc_q, doc_k, ab_block, user=None, b=0, h=0):
     """Rows [q0, q0+len(qb)) of the masked logits plus what the backward needs to redo score_mod."""
     s = (qb @ k.T) * np.float32(sm_scale)
     dsig = None
@@ -88,6 +88,12 @@ def _logits_block(qb, k, *, sm_scale, score_kind, cap, slope, q0, mask_kind, win
     nq, nk = s.shape
     q_idx = np.arange(q0, q0 + nq)
     k_idx = np.arange(nk)
+    if score_kind == "user":
+        # any score function of the scaled score, batch, head and positions (the reference's score_fn branch,
+        # mha_reference.py:44-48, generalised); its derivative plays the part jax.vjp plays in the reference
+        f, df = user
+        t = np.asarray(f(s, b, h, q_idx[:, None], k_idx[None, :]), np.float32)
+        dsig = np.asarray(df(s, b, h, q_idx[:, None], k_idx[None, :]), np.float32) * np.ones_like(s)
     if score_kind == "alibi":
         dist = (q_idx[:, None] - k_idx[None, :]).astype(np.float32)
         t = t - np.float32(slope) * dist
@@ -114,7 +120,7 @@ def _per_head_args(b, h, score_kind, alibi_slopes, doc_ids, ab):
 
 def mha_reference(q, k, v, ab=None, *, sm_scale=1.0, save_residuals=False,
                   mask_kind="none", window=None, stride=None, doc_ids=None,
-                  score_kind="none", cap=None, alibi_slopes=None, block_rows=1024):
+                  score_kind="none", cap=None, alibi_slopes=None, block_rows=1024, user=None):
     """Dense forward.  q,k,v: [B,H,S,D] arrays (any float dtype; computed in f32).
 
     Returns ``o`` (f32) or ``(o, l, m)`` with l = sum exp(x - m), m = row max, both [B,H,Sq] f32
@@ -137,7 +143,7 @@ def mha_reference(q, k, v, ab=None, *, sm_scale=1.0, save_residuals=False,
                                      score_kind=score_kind, cap=cap, slope=slope, q0=q0,
                                      mask_kind=mask_kind, window=window, stride=stride,
                                      doc_q=docs, doc_k=docs,
-                                     ab_block=None if abh is None else abh[q0:q1, :kl])
+                                     ab_block=None if abh is None else abh[q0:q1, :kl], user=user, b=b, h=h)
                 mb = x.max(axis=-1)
                 un = np.exp(x - mb[:, None])
                 lb = un.sum(axis=-1, dtype=np.float32)
@@ -155,7 +161,7 @@ def delta_reference(o, do):
 
 def mha_bwd_reference(q, k, v, o, do, l, m, ab=None, *, sm_scale=1.0,
                       mask_kind="none", window=None, stride=None, doc_ids=None,
-                      score_kind="none", cap=None, alibi_slopes=None, block_rows=1024, return_dab=False):
+                      score_kind="none", cap=None, alibi_slopes=None, block_rows=1024, return_dab=False, user=None):
     """Dense backward mirroring ``mha_reference.py:112-237``.  Returns (dq, dk, dv) in f32, plus the gradient of
     the dense bias ``ab`` ([B,H,Sq,Sk]) with ``return_dab``."""
     q = np.asarray(q, dtype=np.float32)
@@ -182,7 +188,7 @@ def mha_bwd_reference(q, k, v, o, do, l, m, ab=None, *, sm_scale=1.0,
                                         score_kind=score_kind, cap=cap, slope=slope, q0=q0,
                                         mask_kind=mask_kind, window=window, stride=stride,
                                         doc_q=docs, doc_k=docs,
-                                        ab_block=None if abh is None else abh[q0:q1, :kl])
+                                        ab_block=None if abh is None else abh[q0:q1, :kl], user=user, b=b, h=h)
                 lb = l[b, h, q0:q1]
                 l_safe = np.where(lb == 0, np.float32(1.0), lb)       # mha_reference.py:206
                 p = np.exp(x - m[b, h, q0:q1, None]) / l_safe[:, None]

@@ -56,7 +56,7 @@ def make_qkvdo(shape_q, shape_k, seed, dtype, device="cuda"):
     return [t.to(device) for t in ts], host
 
 
-def build_mods(fa, mask_kind, score_kind, *, window=0, stride=0, doc_ids=None, cap=0.0, slopes=None):
+def build_mods(fa, mask_kind, score_kind, *, window=0, stride=0, doc_ids=None, cap=0.0, slopes=None, user_fn=None):
     """(mask_fn, block_mask_fn, score_fn, segment_ids) in the package's vocabulary."""
     M = fa.masks
     seg = None
@@ -79,14 +79,16 @@ def build_mods(fa, mask_kind, score_kind, *, window=0, stride=0, doc_ids=None, c
         sf = fa.scores.make_alibi_score_fn(slopes)
     elif score_kind == "softcap":
         sf = fa.scores.make_softcap_score_fn(cap)
+    elif score_kind == "user":
+        sf = fa.util.make_jax_score_fn(user_fn)     # traced into CUDA, compiled at run time
     return mf, bf, sf, seg
 
 
 def run_hot_path(fa, q, k, v, do, *, sm_scale, mask_kind="none", score_kind="none", backend="auto", window=0,
-                 stride=0, doc_ids=None, cap=0.0, slopes=None, status=None):
+                 stride=0, doc_ids=None, cap=0.0, slopes=None, status=None, user_fn=None):
     """fwd -> delta -> dq -> dkv through the reference-named entry points.  Returns a dict of tensors."""
     mf, bf, sf, seg = build_mods(fa, mask_kind, score_kind, window=window, stride=stride, doc_ids=doc_ids,
-                                 cap=cap, slopes=slopes)
+                                 cap=cap, slopes=slopes, user_fn=user_fn)
     o, l, m = fa._flex_attention_impl(q, k, v, None, seg, True, False, sm_scale, 1, 128, 128, 128, False, bf, mf,
                                       sf, backend=backend, status=status)
     delta = fa.bwd_preprocess(o, do)
@@ -102,9 +104,9 @@ def run_hot_path(fa, q, k, v, do, *, sm_scale, mask_kind="none", score_kind="non
 
 
 def oracle_hot_path(qh, kh, vh, doh, *, sm_scale, mask_kind="none", score_kind="none", window=None, stride=None,
-                    doc_ids=None, cap=None, slopes=None):
+                    doc_ids=None, cap=None, slopes=None, user=None):
     kw = dict(sm_scale=sm_scale, mask_kind=mask_kind, window=window, stride=stride, doc_ids=doc_ids,
-              score_kind=score_kind, cap=cap, alibi_slopes=slopes)
+              score_kind=score_kind, cap=cap, alibi_slopes=slopes, user=user)
     o, l, m = oracle.mha_reference(qh, kh, vh, save_residuals=True, **kw)
     dq, dk, dv = oracle.mha_bwd_reference(qh, kh, vh, o, doh, l, m, **kw)
     return dict(o=o, l=l, m=m, delta=oracle.delta_reference(o, doh), dq=dq, dk=dk, dv=dv)

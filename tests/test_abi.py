@@ -39,7 +39,7 @@ def test_status_strings(B):
     assert B.status_string(0) == "ok"
     assert "workspace" in B.status_string(6)
     assert B.status_string(12345) == "unknown status"
-    assert B.lib.flexattn_abi_version() == 3
+    assert B.lib.flexattn_abi_version() == 4
 
 
 def test_workspace_bytes(B):
@@ -90,7 +90,7 @@ def test_python_layer_rejects_what_the_kernels_cannot_run():
     with pytest.raises(NotImplementedError):
         fa.masks.spec_of(lambda a, b: True)
     with pytest.raises(NotImplementedError):
-        fa.util.make_jax_score_fn(lambda a, b: a @ b.T)
+        fa.util.make_jax_score_fn(lambda a, b: (a @ b.T).sum())      # not an element-wise function of the score
     sf = fa.scores.make_softcap_score_fn(30.0)
     assert fa.util.make_jax_score_fn(sf) is sf
     q = torch.zeros(1, 1, 128, 64)
