@@ -125,9 +125,7 @@ __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, in
 }
 
 template <int D, int SK, int MK>
-// 176 registers per thread: 11 warps x 5632 registers (a warp's registers are allocated in units of 512) fill the
-// register file.  __launch_bounds__(352) alone caps the kernel at 168 and makes the element-wise loops spill.
-__global__ void __maxnreg__(176)
+__global__ void __launch_bounds__(kThreads, 1)
     fwd_pipe_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                           const DevParams P, int* abort_flag) {

@@ -7,11 +7,12 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("kdim", [64, 128])
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 def test_umma_single_tile(variant, kdim):
     from flex_attention_tpu_b200 import _binding as B
     g = torch.Generator().manual_seed(variant * 10 + kdim)
-    a = torch.randn(128, kdim, generator=g).to(torch.bfloat16).cuda()
+    # variants 2 and 3: the A operand is float16 while B stays bfloat16 (generated operand x input tile)
+    a = torch.randn(128, kdim, generator=g).to(torch.float16 if variant >= 2 else torch.bfloat16).cuda()
     if variant == 0:
         b = torch.randn(128, kdim, generator=g).to(torch.bfloat16).cuda()      # [N, K], K contiguous
         want = a.float() @ b.float().T
