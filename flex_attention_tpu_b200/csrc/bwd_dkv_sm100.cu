@@ -10,7 +10,7 @@
 //   S^T  = K Q^T, dP^T = V dO^T      tcgen05.mma, f32 accumulators (128 + 128 TMEM columns)
 //   P^T, dS^T                        in registers; thread = key row, columns = query positions, whose statistics
 //                                    (m log2e + log2 l, delta) are read from shared memory; written back as
-//                                    packed f16 over S^T / dP^T (three more significand bits than bf16)
+//                                    packed bf16 over S^T / dP^T
 //   dV += P^T dO ; dK += dS^T Q      tcgen05.mma, A from tensor memory, B = the dO / Q tile read MN-major
 //
 // The four MMA groups of consecutive tiles are interleaved on the tensor core so that each element-wise phase
@@ -66,7 +66,7 @@ __device__ __forceinline__ void load_stats32(float (&dst)[32], const float* __re
 }
 
 // First element-wise phase, 32 columns: this thread's key row against query columns i_first .. i_first+31.
-// s: raw S^T values in, p * dsigma (the factor dS^T needs) out; pk_p: packed f16 P^T.  The mask functor is
+// s: raw S^T values in, p * dsigma (the factor dS^T needs) out; pk_p: packed bf16 P^T.  The mask functor is
 // compiled in only for partial tiles.
 // what a user score function sees besides the score and the positions
 struct ScoreCtx {
@@ -113,7 +113,7 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
         pv[u] = p;
         s[cc] = __float_as_uint(p * dsig);
       }
-      pk_p[c >> 1] = ptx::pack_f16(pv[0], pv[1]);
+      pk_p[c >> 1] = ptx::pack_bf16_trunc(pv[0], pv[1]);
     }
     return;
   }
@@ -146,13 +146,13 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
       p0 = ((i < seq_q) && mask_keep<MK>(i, j, window, stride, d0, dj)) ? p0 : 0.f;
       p1 = ((i + 1 < seq_q) && mask_keep<MK>(i + 1, j, window, stride, d1, dj)) ? p1 : 0.f;
     }
-    pk_p[c >> 1] = ptx::pack_f16(p0, p1);
+    pk_p[c >> 1] = ptx::pack_bf16_trunc(p0, p1);
     s[c] = __float_as_uint(p0);
     s[c + 1] = __float_as_uint(p1);
   }
 }
 
-// Second phase, 32 columns: dS^T = (p dsigma) * (dP^T - delta), packed f16.
+// Second phase, 32 columns: dS^T = (p dsigma) * (dP^T - delta), packed bf16.
 __device__ __forceinline__ void dkv_ds_math32(const uint32_t (&pd)[32], const uint32_t (&pr)[32],
                                               uint32_t* __restrict__ pk_ds, const float (&dl)[32]) {
 #pragma unroll
@@ -161,7 +161,7 @@ __device__ __forceinline__ void dkv_ds_math32(const uint32_t (&pd)[32], const ui
     const uint64_t pd2 = ptx::pack2(__uint_as_float(pd[c]), __uint_as_float(pd[c + 1]));
     const uint64_t pr2 = ptx::pack2(__uint_as_float(pr[c]), __uint_as_float(pr[c + 1]));
     ptx::unpack2(ptx::mul2(pd2, ptx::sub2(pr2, ptx::pack2(dl[c], dl[c + 1]))), d0, d1);
-    pk_ds[c >> 1] = ptx::pack_f16(d0, d1);
+    pk_ds[c >> 1] = ptx::pack_bf16_trunc(d0, d1);
   }
 }
 
@@ -311,7 +311,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       int fail_at = 1;
       constexpr uint32_t idesc_s = ptx::make_idesc(128, 128, false);
-      constexpr uint32_t idesc_acc = ptx::make_idesc(128, D, true, false, true);  // A = P^T / dS^T, f16
+      constexpr uint32_t idesc_acc = ptx::make_idesc(128, D, true);
       const uint32_t aQ = ptx::smem_u32(sQ), aDO = ptx::smem_u32(sDO);
       const ptx::DescBase bK = ptx::base_kmajor(ptx::smem_u32(sK)), bV = ptx::base_kmajor(ptx::smem_u32(sV));
       auto issue_s = [&](int t) {  // S^T = K Q^T
@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                       idesc_s, kk > 0);
         ptx::mma_commit(&sh->bar_dp);
       };
-      // A operand of the accumulation MMAs: packed f16, 8 columns per K step of 16 query rows; warpgroup w wrote
+      // A operand of the accumulation MMAs: packed bf16, 8 columns per K step of 16 query rows; warpgroup w wrote
       // query columns [64w, 64w+64) at column offset 64w of the S^T / dP^T block.  `first`: the item's first q
       // tile, whose MMA overwrites the accumulator instead of adding to it.
       auto issue_dv = [&](int t, bool first) {  // dV (+)= P^T dO
@@ -451,8 +451,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       auto stage_stats = [&](int n) {
         const int st = (T + n) & 1;
         if (row < 64) {
-          // l == 0 (fully masked row) forces p to 0
-          sh->nlse2[st][64 * half + row] = pf_ok ? (pf_l > 0.f ? -fmaf(pf_m, kLog2e, log2f(pf_l)) : -1.0e30f) : 0.f;
+          // pre-scaled for pack_bf16_trunc; l == 0 (fully masked row) forces p to 0
+          sh->nlse2[st][64 * half + row] =
+              pf_ok ? (pf_l > 0.f ? ptx::kRoundLog2 - fmaf(pf_m, kLog2e, log2f(pf_l)) : -1.0e30f) : ptx::kRoundLog2;
         } else {
           const int r = row - 64;
           const int i = (cm.x + n) * kTile + 64 * half + r;
@@ -514,7 +515,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             dkv_p_math32<SK, MK, false>(sr[1], pk_p + 16, st1, &sh->doc[st][64 * half + 32], i0 + 32, j, dj, P.seq_q,
                                         P.window, P.stride, c2, slope2, abase - 32.f * slope2, capl2, csc, ctx);
           }
-          ptx::tmem_st32(lane_base + colS, pk_p);  // f16 P^T over the first half of this warpgroup's S^T columns
+          ptx::tmem_st32(lane_base + colS, pk_p);  // bf16 P^T over the first half of this warpgroup's S^T columns
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           ptx::mbar_arrive_warp(&sh->bar_p);

@@ -8,7 +8,7 @@
 //   S  = Q K^T, dP = dO V^T         tcgen05.mma, f32 accumulators in tensor memory (128 + 128 columns)
 //   dS = P o (dP - delta) o sigma'  in registers by two warpgroups: threads t and t + 128 own query row t and
 //                                   64 key columns each; P is rebuilt from (l, m) as
-//                                   exp2(x2 - (m log2e + log2 l)); dS is written as f16 to a shared-memory
+//                                   exp2(x2 - (m log2e + log2 l)); dS is written as bf16 to a shared-memory
 //                                   tile in the K-major operand layout
 //   dQ += dS K                      tcgen05.mma, A = dS from shared memory, B = the same K tile read MN-major;
 //                                   dQ (D columns) stays in tensor memory across kv tiles
@@ -45,8 +45,8 @@ struct DqSmem {
   alignas(16) int32_t doc[2][kTile];
 };
 
-// This thread's 64 columns (keys j_first .. j_first+63) of its query row: raw S and dP in, packed f16 dS out.
-// nlse2 = -(m log2e + log2 l) and delta belong to the row; dS is packed as f16.  The mask functor is compiled in only for partial
+// This thread's 64 columns (keys j_first .. j_first+63) of its query row: raw S and dP in, packed bf16 dS out.
+// nlse2 = log2(1 + 2^-9) - (m log2e + log2 l) (pre-scaling for pack_bf16_trunc) and delta belong to the row.  The mask functor is compiled in only for partial
 // tiles.
 // what a user score function sees besides the score and the positions
 struct ScoreCtx {
@@ -100,11 +100,12 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
         }
         const float dt = p * (__uint_as_float(pr[cc >> 5][cc & 31]) - delta);
         if constexpr (kBias) {
-          if (dab_row != nullptr && j_first + cc < seq_k) dab_row[cc] = dt;
+          // p carries the (1 + 2^-9) pre-scaling meant for the truncating bf16 pack: undo it for the f32 gradient
+          if (dab_row != nullptr && j_first + cc < seq_k) dab_row[cc] = dt * ptx::kRoundInv;
         }
         dv[u] = dt * dsig;
       }
-      pk[c >> 1] = ptx::pack_f16(dv[0], dv[1]);
+      pk[c >> 1] = ptx::pack_bf16_trunc(dv[0], dv[1]);
     }
     return;
   }
@@ -144,12 +145,12 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
     float d0f, d1f;
     ptx::unpack2(d2, d0f, d1f);
     if constexpr (kBias) {
-      if (dab_row != nullptr) {  // f32 gradient of the bias
-        if (j_first + c < seq_k) dab_row[c] = d0f;
-        if (j_first + c + 1 < seq_k) dab_row[c + 1] = d1f;
+      if (dab_row != nullptr) {  // f32 gradient of the bias: undo the pre-scaling meant for the truncating bf16 pack
+        if (j_first + c < seq_k) dab_row[c] = d0f * ptx::kRoundInv;
+        if (j_first + c + 1 < seq_k) dab_row[c + 1] = d1f * ptx::kRoundInv;
       }
     }
-    pk[c >> 1] = ptx::pack_f16(d0f, d1f);
+    pk[c >> 1] = ptx::pack_bf16_trunc(d0f, d1f);
   }
 }
 
@@ -161,7 +162,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   constexpr int kPanels = D / 64;
   constexpr uint32_t kTileBytes = kPanels * ptx::kPanelBytes;
   constexpr uint32_t kStageBytes = 2 * kTileBytes;      // [K, V] or [Q, dO]
-  constexpr uint32_t kDsBytes = 2 * ptx::kPanelBytes;   // dS tile: 128 query rows x 128 keys, f16
+  constexpr uint32_t kDsBytes = 2 * ptx::kPanelBytes;   // dS tile: 128 query rows x 128 keys, bf16
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 256;
   constexpr uint32_t kColQ = 384, kColDO = 384 + D / 2;  // Q and dO as packed bf16 A operands (D/2 columns each)
@@ -253,7 +254,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       int fail_at = 1;
       constexpr uint32_t idesc_s = ptx::make_idesc(128, 128, false);
-      constexpr uint32_t idesc_dq = ptx::make_idesc(128, D, true, false, true);  // A = dS, f16
+      constexpr uint32_t idesc_dq = ptx::make_idesc(128, D, true);
       const ptx::DescBase bDS = ptx::base_kmajor(ptx::smem_u32(sDS));
       const uint32_t aRing = ptx::smem_u32(sRing);
       const int total = P.n_qt * P.batch * P.heads, G = (int)gridDim.x, c = (int)blockIdx.x;
@@ -421,8 +422,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (pf_have) { l_ = pf_l; m_ = pf_m; delta = pf_delta; di = pf_di; }
       else row_stats(ia, l_, m_, delta, di);
       pf_have = false;
-      // l == 0 (fully masked row): force p to 0
-      const float nlse2 = row_ok ? (l_ > 0.f ? -fmaf(m_, kLog2e, log2f(l_)) : -1.0e30f) : 0.f;
+      // l == 0 (fully masked row): force p to 0; kRoundLog2 pre-scales p (and so dS) for pack_bf16_trunc
+      const float nlse2 = row_ok ? (l_ > 0.f ? ptx::kRoundLog2 - fmaf(m_, kLog2e, log2f(l_)) : -1.0e30f) : ptx::kRoundLog2;
 
       // dense bias / its gradient: this query row's first element (nullptr: none, or a row past the end)
       const ScoreCtx ctx{P.sm_scale, b, h};

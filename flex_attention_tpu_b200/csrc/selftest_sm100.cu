@@ -41,15 +41,15 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
 
   if (tid == 0) {
     // K-major tiles have kdim / 64 panels, the MN-major B tile ([K, 128]) always two
-    const int a_panels = (variant == 0 || variant == 3) ? panels : 0, b_panels = variant == 0 ? panels : 2;
+    const int a_panels = variant == 0 ? panels : 0, b_panels = variant == 0 ? panels : 2;
     ptx::mbar_arrive_expect_tx(bar_load, (uint32_t)(a_panels + b_panels) * ptx::kPanelBytes);
     for (int p = 0; p < a_panels; ++p) ptx::tma_load_3d(sA + p * ptx::kPanelBytes, &tm_a, bar_load, p * 64, 0, 0);
     for (int p = 0; p < b_panels; ++p) ptx::tma_load_3d(sB + p * ptx::kPanelBytes, &tm_b, bar_load, p * 64, 0, 0);
   }
-  const bool a_tmem = variant == 1 || variant == 2;   // variants 2, 3: A holds f16 instead of bf16 (B stays bf16)
+  const bool a_tmem = variant == 1;
   const bool b_mn = variant != 0;
   if (a_tmem) {
-    // stage A row `tid` into tensor memory as packed 16-bit pairs (element k -> column k/2, low half = even k)
+    // stage A row `tid` into tensor memory as packed bf16 pairs (element k -> column k/2, low half = even k)
     const uint32_t* row = reinterpret_cast<const uint32_t*>(a_glob + (size_t)tid * kdim);
     for (int c0 = 0; c0 < kdim / 2; c0 += 32) {
       uint32_t r[32];
@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
       const int ksteps = kdim / 16;
       // exactly the descriptors of the attention kernels: K-major operands step 32 bytes per K step inside a
       // 128-byte-swizzled panel (LBO 16, SBO 1024); MN-major operands step 2048 bytes (LBO = one panel, SBO 1024)
-      const uint32_t idesc = ptx::make_idesc(128, 128, b_mn, false, variant >= 2);
+      const uint32_t idesc = ptx::make_idesc(128, 128, b_mn);
       for (int kk = 0; kk < ksteps; ++kk) {
         const uint64_t bdesc = b_mn ? ptx::desc_mnmajor(ptx::smem_u32(sB), kk) : ptx::desc_kmajor(ptx::smem_u32(sB), kk);
         if (a_tmem) ptx::mma_ts(tmem + tD, tmem + tA + kk * 8, bdesc, idesc, kk > 0);
@@ -129,7 +129,7 @@ using namespace flexattn;
 extern "C" int flexattn_selftest_umma(void* stream, int variant, const void* a, const void* b, float* d, int32_t kdim,
                                       int32_t* status) {
   if (a == nullptr || b == nullptr || d == nullptr) return FLEXATTN_ERR_NULL_POINTER;
-  if (variant < 0 || variant > 3 || (kdim != 64 && kdim != 128)) return FLEXATTN_ERR_BAD_SHAPE;
+  if ((variant != 0 && variant != 1) || (kdim != 64 && kdim != 128)) return FLEXATTN_ERR_BAD_SHAPE;
   int* af = abort_flag_ptr();
   if (af == nullptr) return FLEXATTN_ERR_CUDA;
   CUtensorMap tm_a, tm_b;

@@ -235,16 +235,14 @@ __host__ __device__ constexpr uint32_t koff_kmajor(int kstep) {
 }
 __host__ __device__ constexpr uint32_t koff_mnmajor(int kstep) { return (uint32_t)kstep * 2048u; }
 
-// Instruction descriptor for kind::f16 with f32 accumulation:
-// [4,6) D format (1 = f32), [7,10) A format (0 = f16, 1 = bf16), [10,13) B format (1 = bf16),
+// Instruction descriptor for kind::f16 with bf16 operands and f32 accumulation:
+// [4,6) D format (1 = f32), [7,10) A format (1 = bf16), [10,13) B format (1 = bf16),
 // bit 15 A major (0 = K), bit 16 B major (0 = K, 1 = MN), [17,23) N >> 3, [24,29) M >> 4.
-// The B operand is always an input tile (bf16).  The A operand is bf16 when it is an input tile too, and may be
-// f16 when the kernel generates it (probabilities, dS): three more significand bits for the same 16 bits, and the
-// values are far inside the f16 range.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major, bool a_mn_major = false,
-                                                  bool a_f16 = false) {
-  return (1u << 4) | ((a_f16 ? 0u : 1u) << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) |
-         ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+// Both operands must have the SAME format: an f16 A operand (format 0) with a bf16 B operand raises an illegal
+// instruction on B200, so operands the kernels generate (probabilities, dS) are bf16 like the input tiles.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major, bool a_mn_major = false) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // Warp-uniform issue helpers.  The MMA / TMA warps run their control loops with all 32 lanes converged and
@@ -339,14 +337,6 @@ __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-// Two f32 -> packed f16 (round to nearest; subnormals kept).  Runs on the conversion / special-function pipe like
-// cvt.rn.bf16x2.f32 below; used for the operands the backward kernels generate (P^T, dS^T, dS), where the three
-// extra significand bits over bf16 decide whether the gradients stay inside the error bound.
-__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
 // cvt.rn.bf16x2.f32 runs on the special-function pipe at a quarter of the FP32 rate (measured: 8 cycles per

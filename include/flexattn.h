@@ -230,9 +230,7 @@ int flexattn_reset_abort(void* stream);
 /* Single-tile tensor-core self checks used by the test-suite (not part of the attention path):
  * D[128,128] = A[128,K] * B^T with A,B bf16 in global memory; `variant` selects the operand
  * staging: 0 = A,B K-major from shared memory; 1 = A from tensor memory (bf16 packed), B MN-major
- * from shared memory (then B is [K,128] row-major); 2 = as 1 with A in f16 (B stays bf16: the operand
- * mix of the backward kernels, whose generated operands are f16); 3 = A in f16, K-major from shared
- * memory, B MN-major.  kdim is 64 or 128.  Output f32 [128,128].
+ * from shared memory (then B is [K,128] row-major).  kdim is 64 or 128.  Output f32 [128,128].
  * The shared-memory descriptors are the ones the attention kernels use.  Replaces nothing in the reference. */
 int flexattn_selftest_umma(void* stream, int variant, const void* a, const void* b, float* d,
                            int32_t kdim, int32_t* status);

@@ -7,12 +7,11 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("kdim", [64, 128])
-@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+@pytest.mark.parametrize("variant", [0, 1])
 def test_umma_single_tile(variant, kdim):
     from flex_attention_tpu_b200 import _binding as B
     g = torch.Generator().manual_seed(variant * 10 + kdim)
-    # variants 2 and 3: the A operand is float16 while B stays bfloat16 (generated operand x input tile)
-    a = torch.randn(128, kdim, generator=g).to(torch.float16 if variant >= 2 else torch.bfloat16).cuda()
+    a = torch.randn(128, kdim, generator=g).to(torch.bfloat16).cuda()
     if variant == 0:
         b = torch.randn(128, kdim, generator=g).to(torch.bfloat16).cuda()      # [N, K], K contiguous
         want = a.float() @ b.float().T
