@@ -76,8 +76,6 @@ DevParams make_dev(const FlexAttnParams* p) {
   d.col_map = reinterpret_cast<const int4*>(ws + L.off_col);
   d.order = reinterpret_cast<const int32_t*>(ws + L.off_order);
   d.order_rm = reinterpret_cast<const int4*>(ws + L.off_order_rm);
-  d.col_order = reinterpret_cast<const int32_t*>(ws + L.off_corder);
-  d.col_order_cm = reinterpret_cast<const int4*>(ws + L.off_corder_cm);
   d.status = p->status;
   d.batch = p->batch; d.heads = p->heads; d.seq_q = p->seq_q; d.seq_k = p->seq_k; d.head_dim = p->head_dim;
   d.n_qt = L.n_qt; d.n_kt = L.n_kt; d.map_rows = L.rows;

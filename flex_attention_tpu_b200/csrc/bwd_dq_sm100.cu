@@ -111,14 +111,17 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
   }
   // two columns per instruction (packed f32x2) wherever the arithmetic allows it
   const uint64_t c22 = ptx::pack2(c2, c2), nl2 = ptx::pack2(nlse2, nlse2), dl2 = ptx::pack2(delta, delta);
+  // ALiBi: the bias of columns (c, c + 1) advances by a constant from pair to pair (one packed add per pair)
+  uint64_t b2 = ptx::pack2(bias0, bias0 + slope2);
+  const uint64_t bstep2 = ptx::pack2(2.f * slope2, 2.f * slope2);
 #pragma unroll
   for (int c = 0; c < 64; c += 2) {
     const uint64_t s2 = ptx::pack2(__uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1]));
     const uint64_t dp2 = ptx::pack2(__uint_as_float(pr[c >> 5][c & 31]), __uint_as_float(pr[c >> 5][(c & 31) + 1]));
     uint64_t arg2;
     if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
-      const uint64_t b2 = ptx::fma2(ptx::pack2((float)c, (float)(c + 1)), ptx::pack2(slope2, slope2), ptx::pack2(bias0, bias0));
       arg2 = ptx::fma2(s2, c22, b2);
+      b2 = ptx::add2(b2, bstep2);
     } else {
       arg2 = ptx::fma2(s2, c22, nl2);
     }

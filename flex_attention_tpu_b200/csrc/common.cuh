@@ -47,7 +47,7 @@ constexpr int32_t kMapMagic = 0x464c5841;  // "FLXA"
 
 struct MapLayout {
   int n_qt, n_kt, rows, n_t;
-  size_t off_row, off_col, off_doc, off_order, off_order_rm, off_corder, off_corder_cm, bytes;
+  size_t off_row, off_col, off_doc, off_order, off_order_rm, bytes;
 };
 
 __host__ __device__ inline MapLayout map_layout(int batch, int seq_q, int seq_k, int mask_kind) {
@@ -65,10 +65,7 @@ __host__ __device__ inline MapLayout map_layout(int batch, int seq_q, int seq_k,
   L.off_order = (L.off_doc + doc + 15) & ~(size_t)15;
   // ... and the row-map entries in that order (so that walking the order needs no dependent load)
   L.off_order_rm = (L.off_order + sizeof(int32_t) * (size_t)L.rows * L.n_qt + 15) & ~(size_t)15;
-  // the same for the kv tiles (ordered by their number of q tiles): work order of the persistent dK/dV kernel
-  L.off_corder = (L.off_order_rm + sizeof(int4) * (size_t)L.rows * L.n_qt + 15) & ~(size_t)15;
-  L.off_corder_cm = (L.off_corder + sizeof(int32_t) * (size_t)L.rows * L.n_kt + 15) & ~(size_t)15;
-  L.bytes = (L.off_corder_cm + sizeof(int4) * (size_t)L.rows * L.n_kt + 255) & ~(size_t)255;
+  L.bytes = (L.off_order_rm + sizeof(int4) * (size_t)L.rows * L.n_qt + 255) & ~(size_t)255;
   return L;
 }
 
@@ -93,8 +90,6 @@ struct DevParams {
   const int4* col_map;  // [rows][n_kt]
   const int32_t* order;  // [rows][n_qt]: q tiles by decreasing number of kv tiles
   const int4* order_rm;  // [rows][n_qt]: row_map entry of order[i]
-  const int32_t* col_order;    // [rows][n_kt]: kv tiles by decreasing number of q tiles
-  const int4* col_order_cm;    // [rows][n_kt]: col_map entry of col_order[i]
   int32_t* status;
   int batch, heads, seq_q, seq_k, head_dim;
   int n_qt, n_kt, map_rows, doc_stride;

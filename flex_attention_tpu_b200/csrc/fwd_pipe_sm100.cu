@@ -89,13 +89,17 @@ __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, in
     return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
   } else {
   // the score arithmetic runs two columns per instruction (packed f32x2); masking and the maximum are scalar
+  // ALiBi: the bias of columns (c, c + 1) advances by a constant from pair to pair: one packed add instead of
+  // rebuilding it from the column numbers
+  uint64_t b2 = ptx::pack2(abase, abase + slope2);
+  const uint64_t bstep2 = ptx::pack2(2.f * slope2, 2.f * slope2);
 #pragma unroll
   for (int c = 0; c < kHalf; c += 2) {
     const uint64_t x2 = ptx::pack2(x[c], x[c + 1]);
     float t0, t1;
     if constexpr (SK == FLEXATTN_SCORE_ALIBI) {
-      const uint64_t b2 = ptx::fma2(ptx::pack2((float)c, (float)(c + 1)), ptx::pack2(slope2, slope2), ptx::pack2(abase, abase));
       ptx::unpack2(ptx::fma2(x2, ptx::pack2(c2, c2), b2), t0, t1);
+      b2 = ptx::add2(b2, bstep2);
     } else {
       ptx::unpack2(ptx::mul2(x2, ptx::pack2(c2, c2)), t0, t1);
     }

@@ -116,8 +116,7 @@ __global__ void mask_map_kernel(MapHeader hdr, MapHeader* __restrict__ hdr_out, 
 }
 
 // Work order of the q tiles of one map row: by decreasing number of kv tiles (counting sort; ties by decreasing
-// tile index, so the result is deterministic).  One CTA per map row; hist has n_kt + 2 entries.  The same kernel
-// orders the kv tiles by their number of q tiles when it is given the column map (n_qt, n_kt swapped).
+// tile index, so the result is deterministic).  One CTA per map row; hist has n_kt + 2 entries.
 __global__ void order_kernel(const int4* __restrict__ row_map, int32_t* __restrict__ order, int4* __restrict__ order_rm,
                              int n_qt, int n_kt) {
   extern __shared__ int hist[];
@@ -166,14 +165,11 @@ cudaError_t launch_mask_map(cudaStream_t st, const FlexAttnParams& p) {
   const int blocks = (entries + 127) / 128;
   mask_map_kernel<<<blocks < 1184 ? blocks : 1184, 128, 0, st>>>(
       hdr, reinterpret_cast<MapHeader*>(ws), reinterpret_cast<int4*>(ws + L.off_row), reinterpret_cast<int4*>(ws + L.off_col), docmm, L.n_t);
-  const size_t hist_bytes = sizeof(int) * (size_t)(L.n_t + 2);
-  if (hist_bytes > 48 * 1024) return cudaErrorInvalidValue;  // more than 12 286 tiles (1.5 M positions)
+  const size_t hist_bytes = sizeof(int) * (size_t)(L.n_kt + 2);
+  if (hist_bytes > 48 * 1024) return cudaErrorInvalidValue;  // more than 12 286 kv tiles (1.5 M keys)
   order_kernel<<<L.rows, 256, hist_bytes, st>>>(reinterpret_cast<const int4*>(ws + L.off_row),
                                                  reinterpret_cast<int32_t*>(ws + L.off_order),
                                                  reinterpret_cast<int4*>(ws + L.off_order_rm), L.n_qt, L.n_kt);
-  order_kernel<<<L.rows, 256, hist_bytes, st>>>(reinterpret_cast<const int4*>(ws + L.off_col),
-                                                 reinterpret_cast<int32_t*>(ws + L.off_corder),
-                                                 reinterpret_cast<int4*>(ws + L.off_corder_cm), L.n_kt, L.n_qt);
   return cudaGetLastError();
 }
 

@@ -382,16 +382,6 @@ __device__ __forceinline__ void load_bias8(float (&b)[8], const float* __restric
     for (int c = 0; c < 8; ++c) b[c] = c < n ? __ldg(p + c) : 0.f;
   }
 }
-// Moves registers between warpgroups at run time (executed by all four warps of a warpgroup): dec releases what the
-// warpgroup holds above N per thread, inc waits until it can own N per thread.
-template <int N>
-__device__ __forceinline__ void setmaxnreg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void setmaxnreg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
