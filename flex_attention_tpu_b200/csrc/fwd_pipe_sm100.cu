@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int s = 0; s < kSBufs; ++s) {
       ptx::mbar_init(&sh->bar_pv[s], 1);
       ptx::mbar_init(&sh->bar_s[s], 1);
-      ptx::mbar_init(&sh->bar_p[s], 256);
+      ptx::mbar_init(&sh->bar_p[s], 8);  // one arrival per softmax warp
     }
     ptx::fence_barrier_init();
   }
@@ -464,7 +464,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
-          ptx::mbar_arrive(&sh->bar_p[sb]);
+          ptx::mbar_arrive_warp(&sh->bar_p[sb]);
         }
         if (++sb == kSBufs) { sb = 0; sph ^= 1u; }
       }

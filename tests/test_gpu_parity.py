@@ -190,6 +190,7 @@ def test_error_is_operand_and_store_rounding():
     e_gpu, e_model = np.abs(gpu - dv).max(), np.abs(model - dv).max()
     print("parity", {"case": "error model dv", "gpu_max_abs": float(e_gpu), "model_max_abs": float(e_model)})
     assert abs(e_gpu - e_model) <= 0.1 * e_model, (e_gpu, e_model)
-    # the GPU accumulates in another order and uses ex2.approx: at most one bf16 rounding step apart from the model
+    # the GPU accumulates in another order and uses ex2.approx: element by element at most two units in the last
+    # place of bf16 apart from the model (a flipped rounding of the stored value, seldom of two)
     from helpers import bf16_half_ulp
-    assert float((np.abs(gpu - model) - 2 * bf16_half_ulp(model)).max()) <= 1e-3
+    assert float((np.abs(gpu - model) - 4 * bf16_half_ulp(model)).max()) <= 0.0
