@@ -67,6 +67,7 @@ WORKLOADS = {
                desc="causal MHA fwd+bwd bf16 B=16 H=64 S=32768 D=128 (BASELINE configs[4])"),
 }
 SUB_WORKLOADS = ("c1", "c2", "c3", "c4", "t_nomask", "t_alibi", "t_softcap")
+E2E_CHUNK_HEADS = 8   # the host-buffer pipeline moves chunks of 8 heads of one batch row (67 MB per tensor at S=8192)
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel, from the ncu captures summarised under
 # profiles/ (None where no capture of the current kernel exists).
@@ -591,18 +592,19 @@ def run_ours(args, w):
             # chunks of the batch flow through copy-in, compute and copy-out streams so that the PCIe transfers
             # overlap the kernels and each other
             host_api.fwd_bwd_from_host(*host_in, sm_scale=hp.sm_scale, mask_fn=hp.mf, block_mask_fn=hp.bf, score_fn=hp.sf,
-                                       segment_ids=hp.seg, out=host_out, chunk_batch=1)
+                                       segment_ids=hp.seg, out=host_out, chunk_batch=1, chunk_heads=E2E_CHUNK_HEADS)
 
         def copy_only_step():
             # the same bytes over the same pinned buffers, both directions at once, no kernels: the ceiling of e2e
             s_in, s_out = copy_streams
             for b0 in range(w["B"]):
-                with torch.cuda.stream(s_in):
-                    for d_, h_ in zip(stage_in, host_in):
-                        d_.copy_(h_[b0:b0 + 1], non_blocking=True)
-                with torch.cuda.stream(s_out):
-                    for h_, d_ in zip(host_out, stage_out):
-                        h_[b0:b0 + 1].copy_(d_, non_blocking=True)
+                for h0 in range(0, w["H"], ch):
+                    with torch.cuda.stream(s_in):
+                        for d_, h_ in zip(stage_in, host_in):
+                            d_.copy_(h_[b0:b0 + 1, h0:h0 + ch], non_blocking=True)
+                    with torch.cuda.stream(s_out):
+                        for h_, d_ in zip(host_out, stage_out):
+                            h_[b0:b0 + 1, h0:h0 + ch].copy_(d_, non_blocking=True)
             for s in copy_streams:
                 torch.cuda.current_stream().wait_stream(s)
             torch.cuda.current_stream().synchronize()
@@ -623,7 +625,8 @@ def run_ours(args, w):
             e2e_step()
         e2e_ms, e2e_wall_ms = timed(e2e_step, e2e_steps)
         copy_streams = (torch.cuda.Stream(), torch.cuda.Stream())
-        stage_in = [torch.empty((1, *t.shape[1:]), dtype=t.dtype, device="cuda") for t in host_in]
+        ch = min(E2E_CHUNK_HEADS, w["H"]) if w["H"] % min(E2E_CHUNK_HEADS, w["H"]) == 0 else w["H"]
+        stage_in = [torch.empty((1, ch, *t.shape[2:]), dtype=t.dtype, device="cuda") for t in host_in]
         stage_out = [torch.empty_like(t) for t in stage_in]
         copy_only_step()
         copy_ms, _ = timed(copy_only_step, e2e_steps)
