@@ -26,7 +26,7 @@
 namespace flexattn {
 namespace FLEXATTN_TU_NAMESPACE {
 
-constexpr int kThreads = 384;  // warps 0-3, 4-7: element-wise warpgroups (64 query columns each); 8: MMA; 9: TMA; 10, 11 idle
+constexpr int kThreads = 320;  // warps 0-3, 4-7: element-wise warpgroups (64 query columns each); 8: MMA; 9: TMA
 constexpr int kMmaWarp = 8, kTmaWarp = 9;
 
 struct DkvSmem {
@@ -205,9 +205,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   ptx::tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
 
-  if (warp >= 8) {
-  // the third warpgroup (single-thread roles and the warps that only complete it) hands registers over
-  ptx::setmaxnreg_dec<88>();
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
     // Q and dO have rings of their own: the Q stage of tile n is free once dK(n) has run, the dO stage once
@@ -331,10 +328,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (ok) ptx::mma_commit(&sh->bar_acc);
       if (!ok) give_up(abort_flag, P.status, 3, fail_at);
     }
-  }
   } else {
     // ------------------------------------------------------------------ element-wise warpgroups
-    ptx::setmaxnreg_inc<208>();
     const int row = tid & 127;        // key row inside the tile = TMEM lane
     const int half = tid >> 7;        // which 64 query columns of every tile this warpgroup handles
     const int j = kt * kTile + row;   // global key position

@@ -29,7 +29,7 @@
 namespace flexattn {
 namespace FLEXATTN_TU_NAMESPACE {
 
-constexpr int kThreads = 384;  // warps 0-3, 4-7: element-wise warpgroups (64 key columns each); 8: MMA; 9: TMA; 10, 11 idle
+constexpr int kThreads = 320;  // warps 0-3, 4-7: element-wise warpgroups (64 key columns each); 8: MMA; 9: TMA
 constexpr int kMmaWarp = 8, kTmaWarp = 9;
 
 constexpr int kStages = 3;
@@ -203,9 +203,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   // In every role: e = index of a ring entry in this CTA's stream (stage e % 3, barrier phase (e / 3) & 1),
   // T = index of a kv tile in the stream (phase T & 1 of the per-tile barriers), r = index of an item.
-  if (warp >= 8) {
-  // the third warpgroup (single-thread roles and the warps that only complete it) hands registers over
-  ptx::setmaxnreg_dec<88>();
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -342,10 +339,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!ok) give_up(abort_flag, P.status, 2, fail_at);
     }
-  }
   } else {
     // ------------------------------------------------------------------ element-wise warpgroups
-    ptx::setmaxnreg_inc<208>();
     const int row = tid & 127;   // query row inside the tile = TMEM lane
     const int half = tid >> 7;   // which 64 key columns of every tile this thread handles
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);

@@ -30,7 +30,7 @@
 namespace flexattn {
 namespace FLEXATTN_TU_NAMESPACE {
 
-constexpr int kThreads = 384;  // warps 0-7: softmax; 8: MMA; 9: TMA for Q and K; 10: TMA for V; 11 idle
+constexpr int kThreads = 352;
 constexpr int kMmaWarp = 8, kTmaWarp = 9, kTmaWarpV = 10;
 constexpr int kHalf = kTile / 2;
 constexpr int kSBufs = 3;
@@ -180,9 +180,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   // previous completion, P V of tile T-3, is known to be done once S of tile T has been read.
   // In every role: T = index of a kv tile in this CTA's stream over all its items, qi = index of an item among
   // the CTA's non-empty items.  Ring stage = index & 1, barrier phase = (index >> 1) & 1 (score buffers: % 3, / 3).
-  if (warp >= 8) {
-  // the third warpgroup (single-thread roles and the warps that only complete it) hands registers over
-  ptx::setmaxnreg_dec<88>();
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer: Q and K
     if (lane == 0) {
@@ -327,10 +324,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!ok) give_up(abort_flag, P.status, 4, fail_at);
     }
-  }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
-    ptx::setmaxnreg_inc<208>();
     const int row = tid & 127;
     const int half = tid >> 7;
     const int c_base = half * kHalf;

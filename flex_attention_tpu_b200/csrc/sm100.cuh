@@ -382,18 +382,6 @@ __device__ __forceinline__ void load_bias8(float (&b)[8], const float* __restric
     for (int c = 0; c < 8; ++c) b[c] = c < n ? __ldg(p + c) : 0.f;
   }
 }
-// Moves registers between warpgroups at run time (executed by all four warps of a warpgroup): dec releases what the
-// warpgroup holds above N per thread, inc waits until it can own N per thread.  A 384-thread kernel starts with 168
-// registers per thread; the single-thread roles (MMA issuer, TMA producers) need few, the 64-column element-wise
-// math wants more: 4 warps x 88 + 8 warps x 208 is the same total.
-template <int N>
-__device__ __forceinline__ void setmaxnreg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void setmaxnreg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
