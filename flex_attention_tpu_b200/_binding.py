@@ -11,7 +11,12 @@ from collections import OrderedDict
 
 import torch
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libflexattn.so")
+# FLEXATTN_DEBUG=1 loads the bounds-checked build of the same library (every direct global-memory access of the
+# tensor-core kernels guarded; an out-of-range index is reported through the status words as code 14 instead of
+# faulting).  Slower; meant for bring-up and for the tests that run without a memory checker.
+DEBUG_BUILD = os.environ.get("FLEXATTN_DEBUG", "0") not in ("", "0")
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)),
+                         "libflexattn_debug.so" if DEBUG_BUILD else "libflexattn.so")
 
 DTYPE_BF16, DTYPE_F32 = 0, 1
 SCORE_NONE, SCORE_ALIBI, SCORE_SOFTCAP, SCORE_USER = 0, 1, 2, 3

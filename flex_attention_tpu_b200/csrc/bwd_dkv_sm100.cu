@@ -337,11 +337,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t colS = kColS + 64 * half, colDP = kColDP + 64 * half;
     const float c2 = P.sm_scale * kLog2e;
-    const float slope2 = (SK == FLEXATTN_SCORE_ALIBI) ? P.alibi_slopes[h] * kLog2e : 0.f;
+    const long long n_rows = (long long)P.batch * P.heads * P.seq_q, n_doc = (long long)P.batch * P.doc_stride;
+    const float slope2 = (SK == FLEXATTN_SCORE_ALIBI && FLEXATTN_DBG_OK(h, P.heads, 3, 301)) ? P.alibi_slopes[h] * kLog2e : 0.f;
     const float capl2 = P.cap * kLog2e;
     const float csc = (SK == FLEXATTN_SCORE_SOFTCAP) ? P.sm_scale / P.cap : 0.f;
     const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
-    const int dj = (MK == FLEXATTN_MASK_DOCUMENT && row_ok) ? doc[j] : -2;
+    const int dj = (MK == FLEXATTN_MASK_DOCUMENT && row_ok && FLEXATTN_DBG_OK((long long)b * P.doc_stride + j, n_doc, 3, 302))
+                       ? doc[j] : -2;
     const ScoreCtx ctx{P.sm_scale, b, h};
     bool ok = true;
     int fail_at = 0;
@@ -370,7 +372,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool pf_ok = false;
     auto fetch_stats = [&](int n) {  // threads 0..63
       const int i = (cm.x + n) * kTile + 64 * half + row;
-      pf_ok = i < P.seq_q;
+      pf_ok = i < P.seq_q && FLEXATTN_DBG_OK((long long)stat_base + i, n_rows, 3, 303);
       if (pf_ok) {
         pf_l = P.l[stat_base + i];
         pf_m = P.m[stat_base + i];
@@ -385,7 +387,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       } else {
         const int r = row - 64;
         const int i = (cm.x + n) * kTile + 64 * half + r;
-        if (i < P.seq_q) {
+        if (i < P.seq_q && FLEXATTN_DBG_OK((long long)stat_base + i, n_rows, 3, 304) &&
+            (MK != FLEXATTN_MASK_DOCUMENT || FLEXATTN_DBG_OK((long long)b * P.doc_stride + i, n_doc, 3, 305))) {
           ptx::cp_async4(&sh->delta[st][64 * half + r], &P.delta[stat_base + i]);
           if (MK == FLEXATTN_MASK_DOCUMENT) ptx::cp_async4(&sh->doc[st][64 * half + r], &doc[i]);
         } else {
@@ -426,7 +429,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         const float abase = slope2 * (float)(j - i0);  // ALiBi bias = slope * (j - i), i = i0 + column
         if (P.ab != nullptr) {
           // element (query i0, key j) of the dense bias; nullptr for a key past the end of the sequence
-          const float* ab_col = row_ok ? P.ab + ((size_t)bh * P.seq_q + i0) * P.seq_k + j : nullptr;
+          const float* ab_col = (row_ok && FLEXATTN_DBG_OK((long long)bh * P.seq_q + i0, n_rows, 3, 306))
+                                    ? P.ab + ((size_t)bh * P.seq_q + i0) * P.seq_k + j : nullptr;
           dkv_p_math32<SK, MK, true, true>(sr[0], pk_p, st0, &sh->doc[st][64 * half], i0, j, dj, P.seq_q, P.window,
                                            P.stride, c2, slope2, abase, capl2, csc, ctx, ab_col, (size_t)P.seq_k);
           dkv_p_math32<SK, MK, true, true>(sr[1], pk_p + 16, st1, &sh->doc[st][64 * half + 32], i0 + 32, j, dj, P.seq_q,

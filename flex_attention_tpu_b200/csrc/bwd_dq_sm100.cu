@@ -360,12 +360,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     auto row_stats = [&](const int4 ia, float& l, float& m, float& dl, int& di_out) {
       const int i = ia.y * kTile + row;
       l = 0.f; m = 0.f; dl = 0.f; di_out = 0;
-      if (i < P.seq_q) {
+      if (i < P.seq_q && FLEXATTN_DBG_OK((long long)ia.x * P.seq_q + i, (long long)P.batch * P.heads * P.seq_q, 2, 201)) {
         const size_t g = (size_t)ia.x * P.seq_q + i;
         l = P.l[g];
         m = P.m[g];
         dl = P.delta[g];
-        if (MK == FLEXATTN_MASK_DOCUMENT) di_out = (P.doc_ids + (size_t)(ia.x / P.heads) * P.doc_stride)[i];
+        if (MK == FLEXATTN_MASK_DOCUMENT &&
+            FLEXATTN_DBG_OK((long long)(ia.x / P.heads) * P.doc_stride + i, (long long)P.batch * P.doc_stride, 2, 202))
+          di_out = (P.doc_ids + (size_t)(ia.x / P.heads) * P.doc_stride)[i];
       }
     };
 
@@ -418,7 +420,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int N = rm.y - rm.x;
       const int i = qt * kTile + row;
       const bool row_ok = i < P.seq_q;
-      const float slope2 = (SK == FLEXATTN_SCORE_ALIBI) ? P.alibi_slopes[h] * kLog2e : 0.f;
+      const long long n_rows = (long long)P.batch * P.heads * P.seq_q, n_doc = (long long)P.batch * P.doc_stride;
+      const float slope2 = (SK == FLEXATTN_SCORE_ALIBI && FLEXATTN_DBG_OK(h, P.heads, 2, 203)) ? P.alibi_slopes[h] * kLog2e : 0.f;
       const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
       float l_, m_, delta;
       int di;
@@ -430,15 +433,16 @@ __global__ void __launch_bounds__(kThreads, 1)
 
       // dense bias / its gradient: this query row's first element (nullptr: none, or a row past the end)
       const ScoreCtx ctx{P.sm_scale, b, h};
-      const float* ab_q = (P.ab != nullptr && row_ok) ? P.ab + ((size_t)bh * P.seq_q + i) * P.seq_k : nullptr;
-      float* dab_q = (P.dab != nullptr && row_ok) ? P.dab + ((size_t)bh * P.seq_q + i) * P.seq_k : nullptr;
+      const bool bias_row_ok = row_ok && FLEXATTN_DBG_OK((long long)bh * P.seq_q + i, n_rows, 2, 204);
+      const float* ab_q = (P.ab != nullptr && bias_row_ok) ? P.ab + ((size_t)bh * P.seq_q + i) * P.seq_k : nullptr;
+      float* dab_q = (P.dab != nullptr && bias_row_ok) ? P.dab + ((size_t)bh * P.seq_q + i) * P.seq_k : nullptr;
       if (P.dab != nullptr) {
         // the bias gradient is dense: the columns of kv tiles this item never visits get their zeros here
         // (warp = row, lanes along the row: coalesced)
         const int kbeg = min(rm.x * kTile, P.seq_k), kend = min(rm.y * kTile, P.seq_k);
         for (int r = warp; r < kTile; r += 8) {
           const int ir = qt * kTile + r;
-          if (ir >= P.seq_q) break;
+          if (ir >= P.seq_q || !FLEXATTN_DBG_OK((long long)bh * P.seq_q + ir, n_rows, 2, 205)) break;
           float* zrow = P.dab + ((size_t)bh * P.seq_q + ir) * P.seq_k;
           for (int j = lane; j < kbeg; j += 32) zrow[j] = 0.f;
           for (int j = kend + lane; j < P.seq_k; j += 32) zrow[j] = 0.f;
@@ -456,7 +460,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (MK == FLEXATTN_MASK_DOCUMENT && partial) {
           if (row < 64) {
             const int j = j0 + row;
-            sh->doc[T & 1][64 * half + row] = (j < P.seq_k) ? doc[j] : -1;
+            sh->doc[T & 1][64 * half + row] =
+                (j < P.seq_k && FLEXATTN_DBG_OK((long long)b * P.doc_stride + j, n_doc, 2, 206)) ? doc[j] : -1;
           }
           ptx::named_bar_sync(1 + half, 128);
         }

@@ -141,15 +141,40 @@ __device__ __forceinline__ float score_dsig(float s, float inv_cap) {
   }
 }
 
-__device__ __forceinline__ void report_timeout(int32_t* status, int kernel_id, int detail) {
+__device__ __forceinline__ void report_status(int32_t* status, int code, int kernel_id, int detail) {
   if (status != nullptr) {
-    if (atomicCAS(status, 0, (int)FLEXATTN_ERR_TIMEOUT) == 0) {
+    if (atomicCAS(status, 0, code) == 0) {
       status[1] = kernel_id;
       status[2] = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
       status[3] = detail;
     }
   }
 }
+__device__ __forceinline__ void report_timeout(int32_t* status, int kernel_id, int detail) {
+  report_status(status, (int)FLEXATTN_ERR_TIMEOUT, kernel_id, detail);
+}
+
+// Bounds-checked build (-DFLEXATTN_DEBUG, libflexattn_debug.so): every direct global-memory access of the
+// tensor-core kernels (everything that does not go through a TMA tensor map, which clips by itself) is guarded.
+// An index outside its array is recorded as {FLEXATTN_ERR_DEBUG_BOUNDS, kernel id, block, site} in the status
+// words and the access is skipped, so a wrong index shows up as a status instead of a memory fault.  In the
+// ordinary build the check is the constant `true` and disappears.
+#ifdef FLEXATTN_DEBUG
+constexpr bool kDebugChecks = true;
+#else
+constexpr bool kDebugChecks = false;
+#endif
+__device__ __forceinline__ bool dbg_in_bounds(long long idx, long long limit, int32_t* status, int kernel_id, int site) {
+  if constexpr (!kDebugChecks) {
+    return true;
+  } else {
+    if (idx >= 0 && idx < limit) return true;
+    report_status(status, (int)FLEXATTN_ERR_DEBUG_BOUNDS, kernel_id, site);
+    return false;
+  }
+}
+#define FLEXATTN_DBG_OK(idx, limit, kernel_id, site) \
+  ::flexattn::dbg_in_bounds((long long)(idx), (long long)(limit), P.status, (kernel_id), (site))
 
 #ifndef FLEXATTN_JIT
 // Host-side validation of a forward call, shared by flexattn_fwd and flexattn_fwd_noalloc (api.cu).

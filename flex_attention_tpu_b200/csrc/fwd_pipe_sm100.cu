@@ -345,12 +345,15 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int4 rm = it.rm;
       const int N = rm.y - rm.x;
       const int i = qt * kTile + row;
-      const float slope2 = (SK == FLEXATTN_SCORE_ALIBI) ? P.alibi_slopes[h] * kLog2e : 0.f;
+      const long long n_rows = (long long)P.batch * P.heads * P.seq_q, n_doc = (long long)P.batch * P.doc_stride;
+      const float slope2 = (SK == FLEXATTN_SCORE_ALIBI && FLEXATTN_DBG_OK(h, P.heads, 4, 101)) ? P.alibi_slopes[h] * kLog2e : 0.f;
       const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
-      const int di = (MK == FLEXATTN_MASK_DOCUMENT && i < P.seq_q) ? doc[i] : 0;
+      const int di = (MK == FLEXATTN_MASK_DOCUMENT && i < P.seq_q && FLEXATTN_DBG_OK((long long)b * P.doc_stride + i, n_doc, 4, 102))
+                         ? doc[i] : 0;
       float m_ref = kMasked, m_true = kMasked, l = 0.f;  // l: sum over this thread's columns only
       // dense bias of this query row (nullptr: no bias, or a row past the end of the sequence)
-      const float* ab_q = (P.ab != nullptr && i < P.seq_q) ? P.ab + ((size_t)bh * P.seq_q + i) * P.seq_k : nullptr;
+      const float* ab_q = (P.ab != nullptr && i < P.seq_q && FLEXATTN_DBG_OK((long long)bh * P.seq_q + i, n_rows, 4, 103))
+                              ? P.ab + ((size_t)bh * P.seq_q + i) * P.seq_k : nullptr;
       const ScoreCtx ctx{P.sm_scale, b, h};
 
       for (int n = 0; n < N; ++n, ++T) {
@@ -360,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const bool partial = P.ab != nullptr || !(kt >= rm.z && kt < rm.w);
         if (MK == FLEXATTN_MASK_DOCUMENT && partial && half == 0) {
           const int j = j0 + row;
-          sh->doc[par][row] = (j < P.seq_k) ? doc[j] : -1;
+          sh->doc[par][row] = (j < P.seq_k && FLEXATTN_DBG_OK((long long)b * P.doc_stride + j, n_doc, 4, 104)) ? doc[j] : -1;
         }
         // A failed wait never leaves the loops early: every thread keeps executing the same named barriers so
         // that nobody is left waiting on one (the time-out path must not be able to hang either).
@@ -519,12 +522,12 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::tma_store_commit();
           o_pending = true;
         }
-      } else if (ok && i < P.seq_q) {  // an item without any kv tile: zeros, written directly
+      } else if (ok && i < P.seq_q && FLEXATTN_DBG_OK(grow, n_rows, 4, 105)) {  // an item without any kv tile: zeros, written directly
         uint16_t* orow = static_cast<uint16_t*>(P.o) + grow * D;   // bf16 elements
         for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 8)
           *reinterpret_cast<uint4*>(orow + c0) = make_uint4(0u, 0u, 0u, 0u);
       }
-      if (ok && half == 0 && i < P.seq_q) {
+      if (ok && half == 0 && i < P.seq_q && FLEXATTN_DBG_OK(grow, n_rows, 4, 106)) {
         P.l[grow] = l * ptx::ex2(m_ref - m_true) * ptx::kRoundInv;
         P.m[grow] = m_true * kLn2;
       }

@@ -171,9 +171,13 @@ int compile_locked(UserScore* u, int which, int head_dim, int mask, const Compil
   if (n.CreateProgram(&prog, src, kKernelFile[which], 5, inc_src, inc_names) != 0) return FLEXATTN_ERR_JIT_COMPILE;
   const std::string expr = std::string("flexattn::jit_tu::") + kKernelName[which] + "<" + std::to_string(head_dim) + ", " +
                            std::to_string((int)FLEXATTN_SCORE_USER) + ", " + std::to_string(mask) + ">";
+#ifdef FLEXATTN_DEBUG
+  const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-DFLEXATTN_JIT=1", "-default-device", "-DFLEXATTN_DEBUG=1"};
+#else
   const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-DFLEXATTN_JIT=1", "-default-device"};
+#endif
   int rc = n.AddNameExpression(prog, expr.c_str());
-  if (rc == 0) rc = n.CompileProgram(prog, 4, opts);
+  if (rc == 0) rc = n.CompileProgram(prog, (int)(sizeof(opts) / sizeof(opts[0])), opts);
   size_t log_size = 0;
   u->log.clear();
   if (n.GetProgramLogSize(prog, &log_size) == 0 && log_size > 1) {

@@ -54,7 +54,8 @@ typedef enum FlexAttnStatus {
   FLEXATTN_ERR_UNSUPPORTED_BACKEND = 10,
   FLEXATTN_ERR_NOALLOC_LIMIT = 11,
   FLEXATTN_ERR_JIT_UNAVAILABLE = 12, /* the run-time compiler (libnvrtc) or the driver's module loader is missing */
-  FLEXATTN_ERR_JIT_COMPILE = 13      /* a user score function did not compile: see flexattn_user_score_log */
+  FLEXATTN_ERR_JIT_COMPILE = 13,     /* a user score function did not compile: see flexattn_user_score_log */
+  FLEXATTN_ERR_DEBUG_BOUNDS = 14     /* bounds-checked build only: a kernel skipped an out-of-range access (status words) */
 } FlexAttnStatus;
 
 typedef enum FlexAttnDType { FLEXATTN_BF16 = 0, FLEXATTN_F32 = 1 } FlexAttnDType;
