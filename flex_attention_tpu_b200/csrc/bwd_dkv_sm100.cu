@@ -428,8 +428,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t pk_p[32];
         const float abase = slope2 * (float)(j - i0);  // ALiBi bias = slope * (j - i), i = i0 + column
         if (P.ab != nullptr) {
-          // element (query i0, key j) of the dense bias; nullptr for a key past the end of the sequence
-          const float* ab_col = (row_ok && FLEXATTN_DBG_OK((long long)bh * P.seq_q + i0, n_rows, 3, 306))
+          // element (query i0, key j) of the dense bias; nullptr for a key past the end of the sequence or when
+          // all 64 queries of this warpgroup lie past the end (the upper half of a ragged last tile)
+          const float* ab_col = (row_ok && i0 < P.seq_q && FLEXATTN_DBG_OK((long long)bh * P.seq_q + i0, n_rows, 3, 306))
                                     ? P.ab + ((size_t)bh * P.seq_q + i0) * P.seq_k + j : nullptr;
           dkv_p_math32<SK, MK, true, true>(sr[0], pk_p, st0, &sh->doc[st][64 * half], i0, j, dj, P.seq_q, P.window,
                                            P.stride, c2, slope2, abase, capl2, csc, ctx, ab_col, (size_t)P.seq_k);

@@ -33,6 +33,7 @@ struct Mods {
   int32_t score_kind;
   float softcap;
   int32_t mask_kind, window, stride, backend;
+  int32_t user_score;  // handle of flexattn_user_score_create (same process, same library instance), else 0
 };
 
 ffi::Error status_to_error(int status, const char* where) {
@@ -69,6 +70,7 @@ ffi::Error describe(FlexAttnParams* p, const ffi::AnyBuffer& q, const ffi::AnyBu
   p->window = mods.window;
   p->stride = mods.stride;
   p->backend = mods.backend;
+  p->user_score = mods.user_score;
   p->doc_ids = doc_ids.size_bytes() > 0 ? static_cast<const int32_t*>(doc_ids.untyped_data()) : nullptr;
   p->alibi_slopes = slopes.size_bytes() > 0 ? static_cast<const float*>(slopes.untyped_data()) : nullptr;
   return ffi::Error::Success();
@@ -84,9 +86,9 @@ ffi::Error bind_and_build_map(cudaStream_t stream, FlexAttnParams* p, ffi::Resul
 ffi::Error Fwd(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi::AnyBuffer v, ffi::AnyBuffer doc_ids,
                ffi::AnyBuffer slopes, ffi::Result<ffi::AnyBuffer> o, ffi::Result<ffi::AnyBuffer> l,
                ffi::Result<ffi::AnyBuffer> m, ffi::Result<ffi::AnyBuffer> ws, float sm_scale, int32_t score_kind,
-               float softcap, int32_t mask_kind, int32_t window, int32_t stride, int32_t backend) {
+               float softcap, int32_t mask_kind, int32_t window, int32_t stride, int32_t backend, int32_t user_score) {
   FlexAttnParams p{};
-  ffi::Error e = describe(&p, q, k, Mods{sm_scale, score_kind, softcap, mask_kind, window, stride, backend}, doc_ids, slopes);
+  ffi::Error e = describe(&p, q, k, Mods{sm_scale, score_kind, softcap, mask_kind, window, stride, backend, user_score}, doc_ids, slopes);
   if (e.failure()) return e;
   p.q = q.untyped_data();
   p.k = k.untyped_data();
@@ -102,7 +104,7 @@ ffi::Error Fwd(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi::Any
 ffi::Error Preprocess(cudaStream_t stream, ffi::AnyBuffer o, ffi::AnyBuffer d_o, ffi::Result<ffi::AnyBuffer> delta) {
   FlexAttnParams p{};
   ffi::AnyBuffer none = o;  // never read: kinds are NONE
-  ffi::Error e = describe(&p, o, o, Mods{1.0f, FLEXATTN_SCORE_NONE, 0.f, FLEXATTN_MASK_NONE, 0, 0, FLEXATTN_BACKEND_AUTO},
+  ffi::Error e = describe(&p, o, o, Mods{1.0f, FLEXATTN_SCORE_NONE, 0.f, FLEXATTN_MASK_NONE, 0, 0, FLEXATTN_BACKEND_AUTO, 0},
                           none, none);
   if (e.failure()) return e;
   p.doc_ids = nullptr;
@@ -116,9 +118,9 @@ ffi::Error Preprocess(cudaStream_t stream, ffi::AnyBuffer o, ffi::AnyBuffer d_o,
 ffi::Error Dq(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi::AnyBuffer v, ffi::AnyBuffer d_o,
               ffi::AnyBuffer l, ffi::AnyBuffer m, ffi::AnyBuffer delta, ffi::AnyBuffer doc_ids, ffi::AnyBuffer slopes,
               ffi::Result<ffi::AnyBuffer> dq, ffi::Result<ffi::AnyBuffer> ws, float sm_scale, int32_t score_kind,
-              float softcap, int32_t mask_kind, int32_t window, int32_t stride, int32_t backend) {
+              float softcap, int32_t mask_kind, int32_t window, int32_t stride, int32_t backend, int32_t user_score) {
   FlexAttnParams p{};
-  ffi::Error e = describe(&p, q, k, Mods{sm_scale, score_kind, softcap, mask_kind, window, stride, backend}, doc_ids, slopes);
+  ffi::Error e = describe(&p, q, k, Mods{sm_scale, score_kind, softcap, mask_kind, window, stride, backend, user_score}, doc_ids, slopes);
   if (e.failure()) return e;
   p.q = q.untyped_data();
   p.k = k.untyped_data();
@@ -137,9 +139,9 @@ ffi::Error Dkv(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi::Any
                ffi::AnyBuffer l, ffi::AnyBuffer m, ffi::AnyBuffer delta, ffi::AnyBuffer doc_ids, ffi::AnyBuffer slopes,
                ffi::Result<ffi::AnyBuffer> dk, ffi::Result<ffi::AnyBuffer> dv, ffi::Result<ffi::AnyBuffer> ws,
                float sm_scale, int32_t score_kind, float softcap, int32_t mask_kind, int32_t window, int32_t stride,
-               int32_t backend) {
+               int32_t backend, int32_t user_score) {
   FlexAttnParams p{};
-  ffi::Error e = describe(&p, q, k, Mods{sm_scale, score_kind, softcap, mask_kind, window, stride, backend}, doc_ids, slopes);
+  ffi::Error e = describe(&p, q, k, Mods{sm_scale, score_kind, softcap, mask_kind, window, stride, backend, user_score}, doc_ids, slopes);
   if (e.failure()) return e;
   p.q = q.untyped_data();
   p.k = k.untyped_data();
@@ -159,7 +161,7 @@ ffi::Error Dkv(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi::Any
 ffi::Error MaskMap(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi::AnyBuffer doc_ids,
                    ffi::Result<ffi::AnyBuffer> ws, int32_t mask_kind, int32_t window, int32_t stride) {
   FlexAttnParams p{};
-  ffi::Error e = describe(&p, q, k, Mods{1.0f, FLEXATTN_SCORE_NONE, 0.f, mask_kind, window, stride, FLEXATTN_BACKEND_AUTO},
+  ffi::Error e = describe(&p, q, k, Mods{1.0f, FLEXATTN_SCORE_NONE, 0.f, mask_kind, window, stride, FLEXATTN_BACKEND_AUTO, 0},
                           doc_ids, doc_ids);
   if (e.failure()) return e;
   p.alibi_slopes = nullptr;
@@ -170,7 +172,7 @@ ffi::Error MaskMap(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi:
 
 #define FLEXATTN_MOD_ATTRS()                                                                                  \
   .Attr<float>("sm_scale").Attr<int32_t>("score_kind").Attr<float>("softcap").Attr<int32_t>("mask_kind")      \
-      .Attr<int32_t>("window").Attr<int32_t>("stride").Attr<int32_t>("backend")
+      .Attr<int32_t>("window").Attr<int32_t>("stride").Attr<int32_t>("backend").Attr<int32_t>("user_score")
 
 XLA_FFI_DEFINE_HANDLER_SYMBOL(flexattn_fwd_ffi, Fwd,
                               ffi::Ffi::Bind()

@@ -24,7 +24,7 @@ _SHIM = os.path.join(_PKG, "libflexattn_xla.so")
 _TARGETS = ("flexattn_fwd_ffi", "flexattn_preprocess_ffi", "flexattn_dq_ffi", "flexattn_dkv_ffi",
             "flexattn_mask_map_ffi")
 _MASK_IDS = {"none": 0, "causal": 1, "sliding_window": 2, "sliding_window_causal": 3, "document": 4, "s2": 5}
-_SCORE_IDS = {"none": 0, "alibi": 1, "softcap": 2}
+_SCORE_IDS = {"none": 0, "alibi": 1, "softcap": 2, "user": 3}
 _registered = False
 
 try:  # pragma: no cover - JAX is not installed everywhere this package is
@@ -76,10 +76,13 @@ def _resolve(q, k, segment_ids, causal, mask_fn, block_mask_fn, score_fn):
         doc = jnp.asarray(segment_ids, jnp.int32)
     slopes = jnp.zeros((0,), jnp.float32)
     attrs = dict(score_kind=np.int32(0), softcap=np.float32(0.0), mask_kind=np.int32(_MASK_IDS[mspec.kind]),
-                 window=np.int32(mspec.window), stride=np.int32(mspec.stride), backend=np.int32(0))
+                 window=np.int32(mspec.window), stride=np.int32(mspec.stride), backend=np.int32(0), user_score=np.int32(0))
     if sspec is not None:
         attrs["score_kind"] = np.int32(_SCORE_IDS[sspec.kind])
         attrs["softcap"] = np.float32(sspec.cap)
+        if sspec.kind == "user":    # traced by util.make_jax_score_fn; registered with the library of this process
+            from . import _binding as B
+            attrs["user_score"] = np.int32(B.user_score_handle(sspec.expr, sspec.dexpr))
         if sspec.kind == "alibi":
             vals = np.asarray(sspec.slopes, np.float32)
             slopes = jnp.asarray(np.broadcast_to(vals, (q.shape[1],)) if vals.size == 1 else vals)
