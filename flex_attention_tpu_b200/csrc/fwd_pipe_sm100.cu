@@ -34,6 +34,15 @@ constexpr int kThreads = 352;
 constexpr int kMmaWarp = 8, kTmaWarp = 9, kTmaWarpV = 10;
 constexpr int kHalf = kTile / 2;
 constexpr int kSBufs = 3;
+
+// Order in which an item's kv tiles are visited.  The ALiBi bias slope * (k_idx - q_idx) grows with the key
+// position, so in ascending order the running row maximum of a steep head rises by more than the lazy-rescale
+// threshold at EVERY tile, and each rescale waits for the previous P V and rewrites O.  Visiting the tiles from the
+// last one down meets the largest bias first and rescales (almost) never; other score kinds keep ascending order.
+template <int SK>
+__device__ __forceinline__ int kv_tile_at(int first, int end, int n) {
+  return SK == FLEXATTN_SCORE_ALIBI ? end - 1 - n : first + n;
+}
 constexpr float kLazyRescale = 8.0f;  // log2 units
 
 struct PipeSmem {
@@ -191,7 +200,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (ItemCursor it(P); ok; it.next(), ++qi) {
         it.skip_empty();
         if (!it.valid()) break;
-        const int bh = it.bh(), first = it.rm.x, N = it.tiles();
+        const int bh = it.bh(), first = it.rm.x, end = it.rm.y, N = it.tiles();
         if (qi >= 1) {  // the buffer holds the Q tile of the previous item: all of its Q K^T MMAs must have completed
           ok = ptx::mbar_wait(&sh->bar_qfree, (qi - 1) & 1);
           if (!ok) { fail_at = 20; break; }
@@ -210,7 +219,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int p = 0; p < kPanels; ++p)
             ptx::tma_load_3d(sK + (T & 1) * kTileBytes + p * ptx::kPanelBytes, &tm_k, &sh->bar_k[T & 1], p * 64,
-                             (first + t) * kTile, bh);
+                             kv_tile_at<SK>(first, end, t) * kTile, bh);
         }
       }
       if (ok) {
@@ -237,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (ItemCursor it(P); ok; it.next()) {
         it.skip_empty();
         if (!it.valid()) break;
-        const int bh = it.bh(), first = it.rm.x, N = it.tiles();
+        const int bh = it.bh(), first = it.rm.x, end = it.rm.y, N = it.tiles();
         for (int t = 0; t < N; ++t, ++T) {
           if (T >= 2) {  // V[T] replaces V[T-2], read by P V of tile T-2
             ok = ptx::mbar_wait(&sh->bar_pv[wsb], wph);
@@ -248,7 +257,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int p = 0; p < kPanels; ++p)
             ptx::tma_load_3d(sV + (T & 1) * kTileBytes + p * ptx::kPanelBytes, &tm_v, &sh->bar_v[T & 1], p * 64,
-                             (first + t) * kTile, bh);
+                             kv_tile_at<SK>(first, end, t) * kTile, bh);
         }
       }
       if (!ok) give_up(abort_flag, P.status, 4, 23);
@@ -359,7 +368,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int n = 0; n < N; ++n, ++T) {
         const uint32_t par = T & 1;
         const uint32_t colS = (uint32_t)sb * 128u;
-        const int kt = rm.x + n, j0 = kt * kTile;
+        const int kt = kv_tile_at<SK>(rm.x, rm.y, n), j0 = kt * kTile;
         const bool partial = P.ab != nullptr || !(kt >= rm.z && kt < rm.w);
         if (MK == FLEXATTN_MASK_DOCUMENT && partial && half == 0) {
           const int j = j0 + row;
