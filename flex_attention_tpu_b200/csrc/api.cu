@@ -167,6 +167,34 @@ int flexattn_build_mask_map(void* stream, const FlexAttnParams* p) {
   return launch_mask_map(static_cast<cudaStream_t>(stream), *p) == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;
 }
 
+namespace {
+// kv tiles an average query tile visits, from the mask kind alone (a document mask depends on the data: 0, which
+// keeps the persistent kernel).
+int mean_kv_tiles(const FlexAttnParams* p) {
+  const int n_kt = (p->seq_k + FLEXATTN_TILE - 1) / FLEXATTN_TILE;
+  const int in_window = p->window / FLEXATTN_TILE + 1;
+  switch (p->mask_kind) {
+    case FLEXATTN_MASK_NONE: return n_kt;
+    case FLEXATTN_MASK_CAUSAL: return (n_kt + 1) / 2;
+    case FLEXATTN_MASK_SLIDING_WINDOW: return n_kt < in_window ? n_kt : (n_kt + in_window) / 2;  // window back, all ahead
+    case FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL: return n_kt < in_window ? n_kt : in_window;
+    case FLEXATTN_MASK_S2: return (n_kt + 1) / 2;  // strided columns keep every tile below the diagonal alive
+    default: return 0;
+  }
+}
+constexpr int kPairMinTiles = 12;  // measured: at 12.5 tiles the two kernels tie, at 16 the pair kernel is 5-12 % faster, at 32 15 %
+int forced_fwd_kernel() {  // 0: choose by shape, 1: two-query-tile kernel, 2: persistent kernel
+  static const int choice = [] {
+    const char* e = getenv("FLEXATTN_FWD_KERNEL");
+    if (e == nullptr) return 0;
+    if (strcmp(e, "pair") == 0) return 1;
+    if (strcmp(e, "pipe") == 0) return 2;
+    return 0;
+  }();
+  return choice;
+}
+}  // namespace
+
 int flexattn_fwd(void* stream, const FlexAttnParams* p) {
   NvtxRange nvtx("flexattn_fwd");
   bool tc = false;
@@ -175,6 +203,14 @@ int flexattn_fwd(void* stream, const FlexAttnParams* p) {
   DevParams d = make_dev(p);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (tc) {
+    // Two tensor-core forward kernels: the persistent one (fwd_pipe_sm100.cu: work items streamed through each CTA,
+    // prologue and epilogue hidden, best for short rows) and the two-query-tile one (fwd_pair_sm100.cu: one row per
+    // thread, K/V shared by two tiles, best once a query tile sees a few dozen kv tiles).  FLEXATTN_FWD_KERNEL=pair
+    // or =pipe in the environment forces one where both can run (read once per process).
+    const bool pair_can = p->score_kind != FLEXATTN_SCORE_USER && p->ab == nullptr;
+    const int forced = forced_fwd_kernel();
+    if (pair_can && (forced == 1 || (forced == 0 && mean_kv_tiles(p) >= kPairMinTiles)))
+      return launch_sm100_fwd_pair(st, d, p->score_kind, p->mask_kind);
     return launch_sm100_fwd_pipe(st, d, p->score_kind, p->mask_kind);
   }
   return launch_simt_fwd(st, d, p->dtype, p->score_kind, p->mask_kind) == cudaSuccess ? FLEXATTN_OK : FLEXATTN_ERR_CUDA;

@@ -190,6 +190,7 @@ cudaError_t launch_simt_dq(cudaStream_t st, const DevParams& d, int dtype, int s
 cudaError_t launch_simt_dkv(cudaStream_t st, const DevParams& d, int dtype, int score, int mask);
 // tensor-core (tcgen05) kernels: bf16, D in {64,128}
 int launch_sm100_fwd_pipe(cudaStream_t st, const DevParams& d, int score, int mask);  // persistent, three score tiles in flight
+int launch_sm100_fwd_pair(cudaStream_t st, const DevParams& d, int score, int mask);  // two query tiles per CTA, one row per thread
 int launch_sm100_dq(cudaStream_t st, const DevParams& d, int score, int mask);
 int launch_sm100_dkv(cudaStream_t st, const DevParams& d, int score, int mask);
 

@@ -66,6 +66,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
 }
 
+// Register reallocation between warpgroups (all four warps of a warpgroup execute it): the element-wise warpgroups
+// of a kernel take the registers its single-lane TMA / MMA warps do not need.  The two calls must sit at the top of
+// the two arms of ONE branch on the warp index, so that the compiler allocates each arm against its own limit.
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
 // One arrival per WARP instead of one per thread: an arrive is a shared-memory atomic, and 32 of them to one
 // address serialise.  Every lane has completed its part (its own tcgen05.wait / fence, then the warp barrier,
 // which orders memory among the lanes); lane 0's arrive then publishes the whole warp's work.  Barriers used
