@@ -152,7 +152,11 @@ size_t flexattn_workspace_bytes(const FlexAttnParams* p);
 int flexattn_build_mask_map(void* stream, const FlexAttnParams* p);
 
 /* Forward.  Replaces `_flex_attention_impl` (flex_attention_kernel.py:66-193) with
- * save_residuals=True: writes o, l, m. */
+ * save_residuals=True: writes o, l, m.  On the tensor-core backend one of two kernels runs, chosen by the mask kind
+ * and the shapes (a persistent one for short rows, a two-query-tile one for long rows); the environment variable
+ * FLEXATTN_FWD_KERNEL=pipe or =pair, read once per process, forces one where both apply.  Their results agree
+ * within the stated tolerance, not bit for bit (the key tiles are summed in the same order but by different
+ * threads). */
 int flexattn_fwd(void* stream, const FlexAttnParams* p);
 
 /* delta = rowsum(o * do).  Replaces the host-side `jnp.sum(o * do, -1)` every reference call site does
