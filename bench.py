@@ -72,7 +72,7 @@ E2E_CHUNK_HEADS = 8   # the host-buffer pipeline moves chunks of 8 heads of one 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel, from the ncu captures summarised under
 # profiles/ (None where no capture of the current kernel exists).
 NCU_TRAFFIC_BYTES = {"c2": {"fwd": 276.4e6, "dq": 369.1e6, "dkv": 380.4e6},
-                     "t": {"fwd": 1559.2e6, "dq": 1837.1e6, "dkv": 1599.5e6}}
+                     "t": {"fwd": 1064.7e6, "dq": 1862.1e6, "dkv": 1599.3e6}}
 
 
 def measured_peaks():
