@@ -58,8 +58,11 @@ CHILD = textwrap.dedent("""
 """)
 
 
-def test_bounds_checked_build_reports_nothing_and_matches_the_oracle():
+@pytest.mark.parametrize("fwd_kernel", ["", "pair"])
+def test_bounds_checked_build_reports_nothing_and_matches_the_oracle(fwd_kernel):
     env = dict(os.environ, FLEXATTN_DEBUG="1")
+    if fwd_kernel:  # the forward kernel for long rows, forced onto these short ones (where it can run)
+        env["FLEXATTN_FWD_KERNEL"] = fwd_kernel
     r = subprocess.run([sys.executable, "-c", CHILD % (ROOT, os.path.join(ROOT, "tests"))], capture_output=True, text=True,
                        timeout=900, env=env)
     assert r.returncode == 0 and "DEBUG_BUILD_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
