@@ -207,7 +207,7 @@ int flexattn_fwd(void* stream, const FlexAttnParams* p) {
     // prologue and epilogue hidden, best for short rows) and the two-query-tile one (fwd_pair_sm100.cu: one row per
     // thread, K/V shared by two tiles, best once a query tile sees a few dozen kv tiles).  FLEXATTN_FWD_KERNEL=pair
     // or =pipe in the environment forces one where both can run (read once per process).
-    const bool pair_can = p->score_kind != FLEXATTN_SCORE_USER && p->ab == nullptr;
+    const bool pair_can = p->ab == nullptr;
     const int forced = forced_fwd_kernel();
     if (pair_can && (forced == 1 || (forced == 0 && mean_kv_tiles(p) >= kPairMinTiles)))
       return launch_sm100_fwd_pair(st, d, p->score_kind, p->mask_kind);

@@ -18,7 +18,7 @@
 #include "sm100.cuh"
 
 namespace flexattn {
-namespace {
+namespace FLEXATTN_TU_NAMESPACE {
 
 constexpr int kThreads = 384;
 constexpr int kMmaWarp = 8, kTmaWarp = 9;
@@ -37,16 +37,24 @@ __device__ __forceinline__ int kv_tile_at(int first, int end, int n) {
   return SK == FLEXATTN_SCORE_ALIBI ? end - 1 - n : first + n;
 }
 
+// what a user score function sees besides the score and the positions
+struct ScoreCtx {
+  float sm_scale;
+  int b, h;
+};
+
 // x: this thread's 128 raw scores of one tile -> log2-domain logits in place; returns their maximum.
 template <int SK, int MK, bool kPartial>
 __device__ __forceinline__ float score_row(float (&x)[kTile], int i, int j0, int seq_k, int window, int stride,
                                            float c2, float slope2, float capl2, float csc, int di,
-                                           const int32_t* s_doc) {
+                                           const int32_t* s_doc, const ScoreCtx ctx) {
   float mx[4] = {kMasked, kMasked, kMasked, kMasked};
-  if constexpr (SK == FLEXATTN_SCORE_SOFTCAP) {
+  if constexpr (SK == FLEXATTN_SCORE_SOFTCAP || SK == FLEXATTN_SCORE_USER) {
 #pragma unroll
     for (int c = 0; c < kTile; ++c) {
-      float t = capl2 * ptx::tanh_approx(x[c] * csc);
+      float t;
+      if constexpr (SK == FLEXATTN_SCORE_USER) t = user_score(x[c] * ctx.sm_scale, ctx.b, ctx.h, i, j0 + c) * kLog2e;
+      else t = capl2 * ptx::tanh_approx(x[c] * csc);
       if constexpr (kPartial) {
         const int j = j0 + c;
         const int dj = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c] : 0;
@@ -285,6 +293,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int di = (MK == FLEXATTN_MASK_DOCUMENT && qt < P.n_qt && i < P.seq_q &&
                     FLEXATTN_DBG_OK((long long)b * P.doc_stride + i, n_doc, 5, 502)) ? doc[i] : 0;
     float m_ref = kMasked, m_true = kMasked, l = 0.f;
+    const ScoreCtx ctx{P.sm_scale, b, h};
     bool ok = true;
     int fail_at = 0;
 
@@ -324,9 +333,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       // scores and folds sm_scale*log2e into the FMA that also subtracts the running max)
       float tmax, xs = 1.0f;
       if (partial) {
-        tmax = score_row<SK, MK, true>(x, i, j0, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di, sh->doc[s]);
+        tmax = score_row<SK, MK, true>(x, i, j0, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di, sh->doc[s], ctx);
       } else if constexpr (SK != FLEXATTN_SCORE_NONE) {
-        tmax = score_row<SK, MK, false>(x, i, j0, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di, sh->doc[s]);
+        tmax = score_row<SK, MK, false>(x, i, j0, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di, sh->doc[s], ctx);
       } else {
         float mx[4] = {x[0], x[1], x[2], x[3]};
 #pragma unroll
@@ -451,6 +460,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+#ifndef FLEXATTN_JIT
 template <int D, int SK, int MK>
 int launch_one(cudaStream_t st, const DevParams& d, const CUtensorMap& tq, const CUtensorMap& tk,
                const CUtensorMap& tv, const CUtensorMap& to, int* abort_flag) {
@@ -491,9 +501,12 @@ int launch_score(cudaStream_t st, const DevParams& d, int score, int mask, const
   }
 }
 
-}  // namespace
+#endif  // !FLEXATTN_JIT
 
-// Built-in score kinds without a dense bias only; the caller keeps the persistent kernel for everything else.
+}  // namespace FLEXATTN_TU_NAMESPACE
+
+#ifndef FLEXATTN_JIT
+// No dense bias here; the caller keeps the persistent kernel for that.
 int launch_sm100_fwd_pair(cudaStream_t st, const DevParams& d, int score, int mask) {
   int* af = abort_flag_ptr();
   if (af == nullptr) return FLEXATTN_ERR_CUDA;
@@ -507,9 +520,17 @@ int launch_sm100_fwd_pair(cudaStream_t st, const DevParams& d, int score, int ma
   if (e) return e;
   e = make_tile_map(&to, d.o, slices, d.seq_q, d.head_dim);
   if (e) return e;
+  if (score == FLEXATTN_SCORE_USER) {
+    // a kernel compiled at run time around the registered score function: same parameters, grid and shared memory
+    const size_t need = 6 * (size_t)(d.head_dim / 64) * ptx::kPanelBytes + sizeof(PairSmem) + 1024;
+    void* args[] = {&tq, &tk, &tv, &to, const_cast<DevParams*>(&d), &af};
+    return jit_launch(3, d.user_score, d.head_dim, mask, (unsigned)((d.n_qt + 1) / 2), (unsigned)(d.batch * d.heads), kThreads,
+                      need > 120 * 1024 ? need : 120 * 1024, st, args);
+  }
   if (d.head_dim == 128) return launch_score<128>(st, d, score, mask, tq, tk, tv, to, af);
   if (d.head_dim == 64) return launch_score<64>(st, d, score, mask, tq, tk, tv, to, af);
   return FLEXATTN_ERR_UNSUPPORTED_HEAD_DIM;
 }
+#endif  // !FLEXATTN_JIT
 
 }  // namespace flexattn

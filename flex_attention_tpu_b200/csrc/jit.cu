@@ -135,8 +135,9 @@ UserScore* find(int handle) {
   return u->alive ? u : nullptr;
 }
 
-const char* const kKernelFile[3] = {"fwd_pipe_sm100.cu", "bwd_dq_sm100.cu", "bwd_dkv_sm100.cu"};
-const char* const kKernelName[3] = {"fwd_pipe_sm100_kernel", "dq_sm100_kernel", "dkv_sm100_kernel"};
+constexpr int kKernels = 4;  // forward (persistent), dQ, dK/dV, forward for long rows
+const char* const kKernelFile[kKernels] = {"fwd_pipe_sm100.cu", "bwd_dq_sm100.cu", "bwd_dkv_sm100.cu", "fwd_pair_sm100.cu"};
+const char* const kKernelName[kKernels] = {"fwd_pipe_sm100_kernel", "dq_sm100_kernel", "dkv_sm100_kernel", "fwd_pair_sm100_kernel"};
 
 const char* embedded(const char* name) {
   for (int i = 0; i < kEmbeddedCount; ++i)
@@ -207,7 +208,7 @@ int compile_locked(UserScore* u, int which, int head_dim, int mask, const Compil
 
 int jit_launch(int which, int handle, int head_dim, int mask, unsigned grid_x, unsigned grid_y, unsigned threads,
                size_t smem_bytes, cudaStream_t st, void** args) {
-  if (which < 0 || which > 2) return FLEXATTN_ERR_UNSUPPORTED_MOD;
+  if (which < 0 || which >= kKernels) return FLEXATTN_ERR_UNSUPPORTED_MOD;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return FLEXATTN_ERR_CUDA;
   const Driver& d = driver();
@@ -278,7 +279,7 @@ extern "C" const char* flexattn_user_score_log(int32_t handle) {
 }
 
 extern "C" int flexattn_user_score_compile(int32_t handle, int which, int32_t head_dim, int32_t mask_kind) {
-  if (which < 0 || which > 2) return FLEXATTN_ERR_UNSUPPORTED_MOD;
+  if (which < 0 || which >= kKernels) return FLEXATTN_ERR_UNSUPPORTED_MOD;
   if (head_dim != 64 && head_dim != 128) return FLEXATTN_ERR_UNSUPPORTED_HEAD_DIM;
   if (mask_kind < FLEXATTN_MASK_NONE || mask_kind > FLEXATTN_MASK_S2) return FLEXATTN_ERR_UNSUPPORTED_MOD;
   std::lock_guard<std::mutex> lock(g_mu);

@@ -223,7 +223,7 @@ int flexattn_user_score_destroy(int32_t handle);
 /* The compiler's log of the most recent failed compilation for `handle` ("" if none).  Valid until the next call
  * that uses the handle.  Never NULL. */
 const char* flexattn_user_score_log(int32_t handle);
-/* Compiles (without loading or launching: needs no GPU) the kernel `which` (0 forward, 1 dQ, 2 dK/dV) for the
+/* Compiles (without loading or launching: needs no GPU) the kernel `which` (0 forward, 1 dQ, 2 dK/dV, 3 forward for long rows) for the
  * handle, head_dim and mask_kind, exactly as the first launch would.  Returns FLEXATTN_OK, or
  * FLEXATTN_ERR_JIT_COMPILE / FLEXATTN_ERR_JIT_UNAVAILABLE.  A test and warm-up hook. */
 int flexattn_user_score_compile(int32_t handle, int which, int32_t head_dim, int32_t mask_kind);

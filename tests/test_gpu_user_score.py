@@ -25,14 +25,16 @@ def _reference_form(q_tile, k_tile):
     return se.where(x >= 0.0, x, 0.5 * x) + 0.1 * se.sigmoid(x)
 
 
+# (the 1700-key unmasked and the 3300-key causal case are long enough for the two-query-tile forward kernel)
 CASES = [("softcap", _softcap, "causal", 128, 777), ("distance", _distance_and_head, "none", 128, 500),
-         ("distance", _distance_and_head, "document", 64, 700), ("leaky", _reference_form, "sliding_window_causal", 128, 640)]
+         ("distance", _distance_and_head, "document", 64, 700), ("leaky", _reference_form, "sliding_window_causal", 128, 640),
+         ("distance", _distance_and_head, "none", 128, 1700), ("softcap", _softcap, "causal", 64, 3300)]
 
 
 @pytest.mark.parametrize("name,fn,mask_kind,D,S", CASES)
 def test_user_score_matches_the_oracle(name, fn, mask_kind, D, S):
     import flex_attention_tpu_b200 as fa
-    B, H = 2, 3
+    B, H = (2, 3) if S < 1500 else (1, 2)
     (q, k, v, do), host = make_qkvdo((B, H, S, D), (B, H, S, D), 1200 + S, torch.bfloat16)
     sf = fa.util.make_jax_score_fn(fn)
     doc = oracle.draw_documents(np.random.default_rng(5), B, S, lo=60, hi=300)[0] if mask_kind == "document" else None
