@@ -108,6 +108,7 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
   // ALiBi: bias = abase - slope2 * column advances by a constant from pair to pair (one packed add per pair)
   uint64_t b2 = ptx::pack2(abase, abase - slope2);
   const uint64_t bstep2 = ptx::pack2(-2.f * slope2, -2.f * slope2);
+  const uint32_t keep = (kPartial && kMaskIsInterval<MK>) ? keep_bits_queries<MK>(j, i_first, seq_q, window) : 0u;
 #pragma unroll
   for (int c = 0; c < 32; c += 2) {
     const uint64_t sv2 = ptx::pack2(__uint_as_float(s[c]), __uint_as_float(s[c + 1]));
@@ -128,7 +129,10 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
       }
     }
     float p0 = ptx::ex2(a0), p1 = ptx::ex2(a1);
-    if constexpr (kPartial) {
+    if constexpr (kPartial && kMaskIsInterval<MK>) {  // `keep`: one bitmap of this key row over the 32 query columns
+      p0 = (keep >> c) & 1u ? p0 : 0.f;
+      p1 = (keep >> (c + 1)) & 1u ? p1 : 0.f;
+    } else if constexpr (kPartial) {
       const int i = i_first + c;
       const int d0 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c] : 0, d1 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c + 1] : 0;
       p0 = ((i < seq_q) && mask_keep<MK>(i, j, window, stride, d0, dj)) ? p0 : 0.f;

@@ -114,6 +114,7 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
   // ALiBi: the bias of columns (c, c + 1) advances by a constant from pair to pair (one packed add per pair)
   uint64_t b2 = ptx::pack2(bias0, bias0 + slope2);
   const uint64_t bstep2 = ptx::pack2(2.f * slope2, 2.f * slope2);
+  uint32_t keep = 0u;  // kept columns of the current group of 32 (interval masks on partial tiles)
 #pragma unroll
   for (int c = 0; c < 64; c += 2) {
     const uint64_t s2 = ptx::pack2(__uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1]));
@@ -138,7 +139,11 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
       a1 = fmaf(bias[(c & 7) + 1], kLog2e, a1);
     }
     float p0 = ptx::ex2(a0), p1 = ptx::ex2(a1);
-    if constexpr (kPartial) {
+    if constexpr (kPartial && kMaskIsInterval<MK>) {  // one bitmap per row and 32 columns instead of per-element tests
+      if ((c & 31) == 0) keep = keep_bits_keys<MK>(i, j_first + c, seq_k, window);
+      p0 = (keep >> (c & 31)) & 1u ? p0 : 0.f;
+      p1 = (keep >> ((c & 31) + 1)) & 1u ? p1 : 0.f;
+    } else if constexpr (kPartial) {
       const int j = j_first + c;
       const int d0 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c] : 0, d1 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c + 1] : 0;
       p0 = ((j < seq_k) && mask_keep<MK>(i, j, window, stride, di, d0)) ? p0 : 0.f;

@@ -119,6 +119,37 @@ __device__ __forceinline__ bool mask_keep(int i, int j, int window, int stride, 
   }
 }
 
+// For the mask kinds whose kept keys of a query row (and kept queries of a key row) form ONE interval, a partial tile
+// evaluates the mask once per row and 32 columns as a bitmap instead of once per element: bit c of the result says
+// whether column `base + c` is kept (the sequence end included).  Document and S2 masks are not intervals.
+template <int MK>
+constexpr bool kMaskIsInterval = MK == FLEXATTN_MASK_NONE || MK == FLEXATTN_MASK_CAUSAL ||
+                                 MK == FLEXATTN_MASK_SLIDING_WINDOW || MK == FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL;
+__device__ __forceinline__ uint32_t range_bits32(int lo, int hi) {  // bits [lo, hi) of a word, clipped to [0, 32)
+  lo = lo > 0 ? lo : 0;
+  hi = hi < 32 ? hi : 32;
+  if (hi <= lo) return 0u;
+  return (hi == 32 ? 0xffffffffu : ((1u << hi) - 1u)) & ~((1u << lo) - 1u);
+}
+// query row i, keys jb .. jb + 31
+template <int MK>
+__device__ __forceinline__ uint32_t keep_bits_keys(int i, int jb, int seq_k, int window) {
+  const bool lower = MK == FLEXATTN_MASK_SLIDING_WINDOW || MK == FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL;  // j > i - window
+  const bool upper = MK == FLEXATTN_MASK_CAUSAL || MK == FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL;           // j <= i
+  const int lo = lower ? i - window + 1 : 0;
+  const int hi = upper ? (i + 1 < seq_k ? i + 1 : seq_k) : seq_k;
+  return range_bits32(lo - jb, hi - jb);
+}
+// key row j, queries ib .. ib + 31
+template <int MK>
+__device__ __forceinline__ uint32_t keep_bits_queries(int j, int ib, int seq_q, int window) {
+  const bool lower = MK == FLEXATTN_MASK_CAUSAL || MK == FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL;           // i >= j
+  const bool upper = MK == FLEXATTN_MASK_SLIDING_WINDOW || MK == FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL;  // i < j + window
+  const int lo = lower ? j : 0;
+  const int hi = upper ? (j + window < seq_q ? j + window : seq_q) : seq_q;
+  return range_bits32(lo - ib, hi - ib);
+}
+
 // Compile-time score functors on the scaled score s = sm_scale * <q,k>, natural units.
 // score_fwd returns t = score_mod(s) + bias(i, j); score_dsig returns d score_mod / d s.
 template <int SK>

@@ -67,6 +67,7 @@ __device__ __forceinline__ float score_row(float (&x)[kTile], int i, int j0, int
     const float abase = slope2 * (float)(j0 - i);
     uint64_t b2 = ptx::pack2(abase, abase + slope2);
     const uint64_t bstep2 = ptx::pack2(2.f * slope2, 2.f * slope2);
+    uint32_t keep = 0u;  // kept columns of the current group of 32 (interval masks on partial tiles)
 #pragma unroll
     for (int c = 0; c < kTile; c += 2) {
       const uint64_t x2 = ptx::pack2(x[c], x[c + 1]);
@@ -77,7 +78,11 @@ __device__ __forceinline__ float score_row(float (&x)[kTile], int i, int j0, int
       } else {
         ptx::unpack2(ptx::mul2(x2, ptx::pack2(c2, c2)), t0, t1);
       }
-      if constexpr (kPartial) {
+      if constexpr (kPartial && kMaskIsInterval<MK>) {  // one bitmap per row and 32 columns instead of per-element tests
+        if ((c & 31) == 0) keep = keep_bits_keys<MK>(i, j0 + c, seq_k, window);
+        t0 = (keep >> (c & 31)) & 1u ? t0 : kMasked;
+        t1 = (keep >> ((c & 31) + 1)) & 1u ? t1 : kMasked;
+      } else if constexpr (kPartial) {
         const int j = j0 + c;
         const int d0 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c] : 0;
         const int d1 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c + 1] : 0;

@@ -102,6 +102,7 @@ __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, in
   // rebuilding it from the column numbers
   uint64_t b2 = ptx::pack2(abase, abase + slope2);
   const uint64_t bstep2 = ptx::pack2(2.f * slope2, 2.f * slope2);
+  uint32_t keep = 0u;  // kept columns of the current group of 32 (interval masks on partial tiles)
 #pragma unroll
   for (int c = 0; c < kHalf; c += 2) {
     const uint64_t x2 = ptx::pack2(x[c], x[c + 1]);
@@ -122,7 +123,11 @@ __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, in
       t0 = fmaf(bias[c & 7], kLog2e, t0);
       t1 = fmaf(bias[(c & 7) + 1], kLog2e, t1);
     }
-    if constexpr (kPartial) {
+    if constexpr (kPartial && kMaskIsInterval<MK>) {
+      if ((c & 31) == 0) keep = keep_bits_keys<MK>(i, j0 + c_base + c, seq_k, window);
+      t0 = (keep >> (c & 31)) & 1u ? t0 : kMasked;
+      t1 = (keep >> ((c & 31) + 1)) & 1u ? t1 : kMasked;
+    } else if constexpr (kPartial) {
       const int j = j0 + c_base + c;
       const int d0 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c_base + c] : 0;
       const int d1 = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c_base + c + 1] : 0;
