@@ -87,6 +87,11 @@ DevParams make_dev(const FlexAttnParams* p) {
   d.col_map = reinterpret_cast<const int4*>(ws + L.off_col);
   d.order = reinterpret_cast<const int32_t*>(ws + L.off_order);
   d.order_rm = reinterpret_cast<const int4*>(ws + L.off_order_rm);
+  if (p->mask_kind == FLEXATTN_MASK_DOCUMENT) {
+    d.run_lo = reinterpret_cast<const int32_t*>(ws + L.off_run_lo);
+    d.run_hi = reinterpret_cast<const int32_t*>(ws + L.off_run_hi);
+    d.doc_sorted = reinterpret_cast<const int32_t*>(ws + L.off_sorted);
+  }
   d.status = p->status;
   d.batch = p->batch; d.heads = p->heads; d.seq_q = p->seq_q; d.seq_k = p->seq_k; d.head_dim = p->head_dim;
   d.n_qt = L.n_qt; d.n_kt = L.n_kt; d.map_rows = L.rows;

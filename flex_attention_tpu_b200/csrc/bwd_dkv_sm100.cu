@@ -63,12 +63,15 @@ struct ScoreCtx {
 // kBias: ab_col points at the dense bias element (query i_first, key j) of this thread's key (nullptr: none, or a
 // key past the end); consecutive queries are ab_stride floats apart, so a warp (32 consecutive keys) reads 128
 // contiguous bytes per query.
-template <int SK, int MK, bool kPartial, bool kBias = false>
+// kInterval: the key row's kept queries are the interval [qlo, qhi) (interval mask kinds; documents over sorted
+// ids): a partial tile then tests one bit per element of a bitmap of the 32 columns.
+template <int SK, int MK, bool kPartial, bool kBias = false, bool kInterval = kMaskIsInterval<MK>>
 __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __restrict__ pk_p, const float (&nl)[32],
                                              const int32_t* __restrict__ s_doc, int i_first, int j, int dj, int seq_q,
                                              int window, int stride, float c2, float slope2, float abase, float capl2,
                                              float csc, const ScoreCtx ctx, const float* __restrict__ ab_col = nullptr,
-                                             size_t ab_stride = 0) {
+                                             size_t ab_stride = 0, int qlo = 0, int qhi = 0) {
+  const uint32_t keep = (kPartial && kInterval) ? range_bits32(qlo - i_first, qhi - i_first) : 0u;
   if constexpr (SK == FLEXATTN_SCORE_SOFTCAP || SK == FLEXATTN_SCORE_USER) {
     // scalar form: the packed one costs registers here (tanh, its derivative and the mask live together)
 #pragma unroll
@@ -91,7 +94,9 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
           if (ab_col != nullptr && i_first + cc < seq_q) arg = fmaf(__ldg(ab_col + (size_t)cc * ab_stride), kLog2e, arg);
         }
         float p = ptx::ex2(arg);
-        if constexpr (kPartial) {
+        if constexpr (kPartial && kInterval) {
+          p = (keep >> cc) & 1u ? p : 0.f;
+        } else if constexpr (kPartial) {
           const int i = i_first + cc;
           const int di = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[cc] : 0;
           p = ((i < seq_q) && mask_keep<MK>(i, j, window, stride, di, dj)) ? p : 0.f;
@@ -108,7 +113,6 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
   // ALiBi: bias = abase - slope2 * column advances by a constant from pair to pair (one packed add per pair)
   uint64_t b2 = ptx::pack2(abase, abase - slope2);
   const uint64_t bstep2 = ptx::pack2(-2.f * slope2, -2.f * slope2);
-  const uint32_t keep = (kPartial && kMaskIsInterval<MK>) ? keep_bits_queries<MK>(j, i_first, seq_q, window) : 0u;
 #pragma unroll
   for (int c = 0; c < 32; c += 2) {
     const uint64_t sv2 = ptx::pack2(__uint_as_float(s[c]), __uint_as_float(s[c + 1]));
@@ -129,7 +133,7 @@ __device__ __forceinline__ void dkv_p_math32(uint32_t (&s)[32], uint32_t* __rest
       }
     }
     float p0 = ptx::ex2(a0), p1 = ptx::ex2(a1);
-    if constexpr (kPartial && kMaskIsInterval<MK>) {  // `keep`: one bitmap of this key row over the 32 query columns
+    if constexpr (kPartial && kInterval) {  // `keep`: one bitmap of this key row over the 32 query columns
       p0 = (keep >> c) & 1u ? p0 : 0.f;
       p1 = (keep >> (c + 1)) & 1u ? p1 : 0.f;
     } else if constexpr (kPartial) {
@@ -349,6 +353,21 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int dj = (MK == FLEXATTN_MASK_DOCUMENT && row_ok && FLEXATTN_DBG_OK((long long)b * P.doc_stride + j, n_doc, 3, 302))
                        ? doc[j] : -2;
     const ScoreCtx ctx{P.sm_scale, b, h};
+    // the interval [qlo, qhi) of queries this key row keeps, where the mask has one: the interval kinds, and a
+    // document mask when the ids of the batch row never decrease (the mask map then holds the end of every key's
+    // document); a key past the end keeps nothing
+    constexpr bool kDoc = MK == FLEXATTN_MASK_DOCUMENT;
+    bool doc_runs = false;
+    int qlo = 0, qhi = 0;
+    if constexpr (kMaskIsInterval<MK>) row_query_interval<MK>(j, P.seq_q, P.window, qlo, qhi);
+    if constexpr (kDoc) {
+      doc_runs = FLEXATTN_DBG_OK(b, P.batch, 3, 307) && P.doc_sorted[b] != 0;
+      if (doc_runs && row_ok && FLEXATTN_DBG_OK((long long)b * P.doc_stride + j, n_doc, 3, 308)) {
+        const int end = P.run_hi[(size_t)b * P.doc_stride + j];
+        qlo = j;
+        qhi = end < P.seq_q ? end : P.seq_q;
+      }
+    }
     bool ok = true;
     int fail_at = 0;
 
@@ -431,26 +450,57 @@ __global__ void __launch_bounds__(kThreads, 1)
       {
         uint32_t pk_p[32];
         const float abase = slope2 * (float)(j - i0);  // ALiBi bias = slope * (j - i), i = i0 + column
+        const float abase1 = abase - 32.f * slope2;
+        const int32_t* d0p = &sh->doc[st][64 * half];
+        const int32_t* d1p = d0p + 32;
         if (P.ab != nullptr) {
           // element (query i0, key j) of the dense bias; nullptr for a key past the end of the sequence or when
           // all 64 queries of this warpgroup lie past the end (the upper half of a ragged last tile)
           const float* ab_col = (row_ok && i0 < P.seq_q && FLEXATTN_DBG_OK((long long)bh * P.seq_q + i0, n_rows, 3, 306))
                                     ? P.ab + ((size_t)bh * P.seq_q + i0) * P.seq_k + j : nullptr;
-          dkv_p_math32<SK, MK, true, true>(sr[0], pk_p, st0, &sh->doc[st][64 * half], i0, j, dj, P.seq_q, P.window,
-                                           P.stride, c2, slope2, abase, capl2, csc, ctx, ab_col, (size_t)P.seq_k);
-          dkv_p_math32<SK, MK, true, true>(sr[1], pk_p + 16, st1, &sh->doc[st][64 * half + 32], i0 + 32, j, dj, P.seq_q,
-                                           P.window, P.stride, c2, slope2, abase - 32.f * slope2, capl2, csc, ctx,
-                                           ab_col != nullptr ? ab_col + 32 * (size_t)P.seq_k : nullptr, (size_t)P.seq_k);
+          const float* ab_col1 = ab_col != nullptr ? ab_col + 32 * (size_t)P.seq_k : nullptr;
+          if constexpr (kDoc) {
+            if (doc_runs) {
+              dkv_p_math32<SK, MK, true, true, true>(sr[0], pk_p, st0, d0p, i0, j, dj, P.seq_q, P.window, P.stride, c2, slope2,
+                                                     abase, capl2, csc, ctx, ab_col, (size_t)P.seq_k, qlo, qhi);
+              dkv_p_math32<SK, MK, true, true, true>(sr[1], pk_p + 16, st1, d1p, i0 + 32, j, dj, P.seq_q, P.window, P.stride, c2,
+                                                     slope2, abase1, capl2, csc, ctx, ab_col1, (size_t)P.seq_k, qlo, qhi);
+            } else {
+              dkv_p_math32<SK, MK, true, true, false>(sr[0], pk_p, st0, d0p, i0, j, dj, P.seq_q, P.window, P.stride, c2, slope2,
+                                                      abase, capl2, csc, ctx, ab_col, (size_t)P.seq_k);
+              dkv_p_math32<SK, MK, true, true, false>(sr[1], pk_p + 16, st1, d1p, i0 + 32, j, dj, P.seq_q, P.window, P.stride, c2,
+                                                      slope2, abase1, capl2, csc, ctx, ab_col1, (size_t)P.seq_k);
+            }
+          } else {
+            dkv_p_math32<SK, MK, true, true>(sr[0], pk_p, st0, d0p, i0, j, dj, P.seq_q, P.window, P.stride, c2, slope2, abase,
+                                             capl2, csc, ctx, ab_col, (size_t)P.seq_k, qlo, qhi);
+            dkv_p_math32<SK, MK, true, true>(sr[1], pk_p + 16, st1, d1p, i0 + 32, j, dj, P.seq_q, P.window, P.stride, c2, slope2,
+                                             abase1, capl2, csc, ctx, ab_col1, (size_t)P.seq_k, qlo, qhi);
+          }
         } else if (partial) {
-          dkv_p_math32<SK, MK, true>(sr[0], pk_p, st0, &sh->doc[st][64 * half], i0, j, dj, P.seq_q, P.window,
-                                     P.stride, c2, slope2, abase, capl2, csc, ctx);
-          dkv_p_math32<SK, MK, true>(sr[1], pk_p + 16, st1, &sh->doc[st][64 * half + 32], i0 + 32, j, dj, P.seq_q,
-                                     P.window, P.stride, c2, slope2, abase - 32.f * slope2, capl2, csc, ctx);
+          if constexpr (kDoc) {
+            if (doc_runs) {
+              dkv_p_math32<SK, MK, true, false, true>(sr[0], pk_p, st0, d0p, i0, j, dj, P.seq_q, P.window, P.stride, c2, slope2,
+                                                      abase, capl2, csc, ctx, nullptr, 0, qlo, qhi);
+              dkv_p_math32<SK, MK, true, false, true>(sr[1], pk_p + 16, st1, d1p, i0 + 32, j, dj, P.seq_q, P.window, P.stride,
+                                                      c2, slope2, abase1, capl2, csc, ctx, nullptr, 0, qlo, qhi);
+            } else {
+              dkv_p_math32<SK, MK, true, false, false>(sr[0], pk_p, st0, d0p, i0, j, dj, P.seq_q, P.window, P.stride, c2, slope2,
+                                                       abase, capl2, csc, ctx);
+              dkv_p_math32<SK, MK, true, false, false>(sr[1], pk_p + 16, st1, d1p, i0 + 32, j, dj, P.seq_q, P.window, P.stride,
+                                                       c2, slope2, abase1, capl2, csc, ctx);
+            }
+          } else {
+            dkv_p_math32<SK, MK, true>(sr[0], pk_p, st0, d0p, i0, j, dj, P.seq_q, P.window, P.stride, c2, slope2, abase, capl2,
+                                       csc, ctx, nullptr, 0, qlo, qhi);
+            dkv_p_math32<SK, MK, true>(sr[1], pk_p + 16, st1, d1p, i0 + 32, j, dj, P.seq_q, P.window, P.stride, c2, slope2,
+                                       abase1, capl2, csc, ctx, nullptr, 0, qlo, qhi);
+          }
         } else {
-          dkv_p_math32<SK, MK, false>(sr[0], pk_p, st0, &sh->doc[st][64 * half], i0, j, dj, P.seq_q, P.window,
-                                      P.stride, c2, slope2, abase, capl2, csc, ctx);
-          dkv_p_math32<SK, MK, false>(sr[1], pk_p + 16, st1, &sh->doc[st][64 * half + 32], i0 + 32, j, dj, P.seq_q,
-                                      P.window, P.stride, c2, slope2, abase - 32.f * slope2, capl2, csc, ctx);
+          dkv_p_math32<SK, MK, false>(sr[0], pk_p, st0, d0p, i0, j, dj, P.seq_q, P.window, P.stride, c2, slope2, abase, capl2,
+                                      csc, ctx);
+          dkv_p_math32<SK, MK, false>(sr[1], pk_p + 16, st1, d1p, i0 + 32, j, dj, P.seq_q, P.window, P.stride, c2, slope2,
+                                      abase1, capl2, csc, ctx);
         }
         ptx::tmem_st32(lane_base + colS, pk_p);  // bf16 P^T over the first half of this warpgroup's S^T columns
         ptx::tmem_wait_st();

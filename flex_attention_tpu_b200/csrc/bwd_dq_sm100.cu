@@ -54,14 +54,17 @@ struct ScoreCtx {
   int b, h;
 };
 
-template <int SK, int MK, bool kPartial, bool kBias = false>
+// kInterval: the row's kept keys are the interval [klo, khi) (interval mask kinds; documents over sorted ids): a
+// partial tile then tests one bit per element of a bitmap built once per 32 columns.
+template <int SK, int MK, bool kPartial, bool kBias = false, bool kInterval = kMaskIsInterval<MK>>
 __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const uint32_t (&pr)[2][32],
                                              uint32_t (&pk)[32], float nlse2, float delta,
                                              const int32_t* __restrict__ s_doc, int i, int di, int j_first, int seq_k,
                                              int window, int stride, float c2, float slope2, float abase, float capl2,
                                              float csc, const ScoreCtx ctx, const float* __restrict__ ab_row = nullptr,
-                                             float* __restrict__ dab_row = nullptr) {
+                                             float* __restrict__ dab_row = nullptr, int klo = 0, int khi = 0) {
   const float bias0 = abase + nlse2;  // ALiBi: slope * (j_first - i), folded with the row's -lse2
+  uint32_t keep = 0u;  // kept columns of the current group of 32 (kInterval on partial tiles)
   // kBias: ab_row / dab_row point at this row's element of column j_first (nullptr: none, or a row past the end);
   // the bias joins the logit after the score function, and its gradient is p * (dp - delta) before sigma'.
   float bias[8];
@@ -93,7 +96,10 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
           arg = fmaf(bias[cc & 7], kLog2e, arg);
         }
         float p = ptx::ex2(arg);
-        if constexpr (kPartial) {
+        if constexpr (kPartial && kInterval) {
+          if ((cc & 31) == 0) keep = range_bits32(klo - (j_first + cc), khi - (j_first + cc));
+          p = (keep >> (cc & 31)) & 1u ? p : 0.f;
+        } else if constexpr (kPartial) {
           const int j = j_first + cc;
           const int dj = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[cc] : 0;
           p = ((j < seq_k) && mask_keep<MK>(i, j, window, stride, di, dj)) ? p : 0.f;
@@ -114,7 +120,6 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
   // ALiBi: the bias of columns (c, c + 1) advances by a constant from pair to pair (one packed add per pair)
   uint64_t b2 = ptx::pack2(bias0, bias0 + slope2);
   const uint64_t bstep2 = ptx::pack2(2.f * slope2, 2.f * slope2);
-  uint32_t keep = 0u;  // kept columns of the current group of 32 (interval masks on partial tiles)
 #pragma unroll
   for (int c = 0; c < 64; c += 2) {
     const uint64_t s2 = ptx::pack2(__uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[c >> 5][(c & 31) + 1]));
@@ -139,8 +144,8 @@ __device__ __forceinline__ void dq_half_math(const uint32_t (&sr)[2][32], const 
       a1 = fmaf(bias[(c & 7) + 1], kLog2e, a1);
     }
     float p0 = ptx::ex2(a0), p1 = ptx::ex2(a1);
-    if constexpr (kPartial && kMaskIsInterval<MK>) {  // one bitmap per row and 32 columns instead of per-element tests
-      if ((c & 31) == 0) keep = keep_bits_keys<MK>(i, j_first + c, seq_k, window);
+    if constexpr (kPartial && kInterval) {  // one bitmap per row and 32 columns instead of per-element tests
+      if ((c & 31) == 0) keep = range_bits32(klo - (j_first + c), khi - (j_first + c));
       p0 = (keep >> (c & 31)) & 1u ? p0 : 0.f;
       p1 = (keep >> ((c & 31) + 1)) & 1u ? p1 : 0.f;
     } else if constexpr (kPartial) {
@@ -436,6 +441,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       // l == 0 (fully masked row): force p to 0; kRoundLog2 pre-scales p (and so dS) for pack_bf16_trunc
       const float nlse2 = row_ok ? (l_ > 0.f ? ptx::kRoundLog2 - fmaf(m_, kLog2e, log2f(l_)) : -1.0e30f) : ptx::kRoundLog2;
 
+      // the interval [klo, khi) of keys this row keeps, where the mask has one: the interval kinds, and a document
+      // mask when the ids of the batch row never decrease (then the mask map holds the start of every row's document)
+      constexpr bool kDoc = MK == FLEXATTN_MASK_DOCUMENT;
+      bool doc_runs = false;
+      int klo = 0, khi = P.seq_k;
+      if constexpr (kMaskIsInterval<MK>) row_key_interval<MK>(i, P.seq_k, P.window, klo, khi);
+      if constexpr (kDoc) {
+        doc_runs = FLEXATTN_DBG_OK(b, P.batch, 2, 207) && P.doc_sorted[b] != 0;
+        if (doc_runs && row_ok && FLEXATTN_DBG_OK((long long)b * P.doc_stride + i, n_doc, 2, 208)) {
+          klo = P.run_lo[(size_t)b * P.doc_stride + i];
+          khi = i + 1 < P.seq_k ? i + 1 : P.seq_k;
+        }
+      }
+
       // dense bias / its gradient: this query row's first element (nullptr: none, or a row past the end)
       const ScoreCtx ctx{P.sm_scale, b, h};
       const bool bias_row_ok = row_ok && FLEXATTN_DBG_OK((long long)bh * P.seq_q + i, n_rows, 2, 204);
@@ -462,7 +481,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int n = 0; n < N; ++n, ++T, ++e) {
         const int kt = rm.x + n, j0 = kt * kTile + 64 * half;  // first key position of this thread's columns
         const bool partial = has_bias || !(kt >= rm.z && kt < rm.w);  // with a bias: always the masked form
-        if (MK == FLEXATTN_MASK_DOCUMENT && partial) {
+        if (MK == FLEXATTN_MASK_DOCUMENT && partial && !doc_runs) {
           if (row < 64) {
             const int j = j0 + row;
             sh->doc[T & 1][64 * half + row] =
@@ -502,16 +521,37 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::mbar_arrive_warp(&sh->bar_ld);  // S / dP columns may be overwritten by the next tile's MMAs
         uint32_t pk[32];
         const float abase = slope2 * (float)(j0 - i);
-        if (has_bias)
-          dq_half_math<SK, MK, true, true>(sr, pr, pk, nlse2, delta, &sh->doc[T & 1][64 * half], i, di, j0, P.seq_k,
-                                           P.window, P.stride, c2, slope2, abase, capl2, csc, ctx,
-                                           ab_q != nullptr ? ab_q + j0 : nullptr, dab_q != nullptr ? dab_q + j0 : nullptr);
-        else if (partial)
-          dq_half_math<SK, MK, true>(sr, pr, pk, nlse2, delta, &sh->doc[T & 1][64 * half], i, di, j0, P.seq_k, P.window,
-                                     P.stride, c2, slope2, abase, capl2, csc, ctx);
-        else
-          dq_half_math<SK, MK, false>(sr, pr, pk, nlse2, delta, &sh->doc[T & 1][64 * half], i, di, j0, P.seq_k, P.window,
-                                      P.stride, c2, slope2, abase, capl2, csc, ctx);
+        const int32_t* s_doc = &sh->doc[T & 1][64 * half];
+        const float* ab_t = ab_q != nullptr ? ab_q + j0 : nullptr;
+        float* dab_t = dab_q != nullptr ? dab_q + j0 : nullptr;
+        if (has_bias) {
+          if constexpr (kDoc) {
+            if (doc_runs)
+              dq_half_math<SK, MK, true, true, true>(sr, pr, pk, nlse2, delta, s_doc, i, di, j0, P.seq_k, P.window, P.stride,
+                                                     c2, slope2, abase, capl2, csc, ctx, ab_t, dab_t, klo, khi);
+            else
+              dq_half_math<SK, MK, true, true, false>(sr, pr, pk, nlse2, delta, s_doc, i, di, j0, P.seq_k, P.window, P.stride,
+                                                      c2, slope2, abase, capl2, csc, ctx, ab_t, dab_t);
+          } else {
+            dq_half_math<SK, MK, true, true>(sr, pr, pk, nlse2, delta, s_doc, i, di, j0, P.seq_k, P.window, P.stride, c2,
+                                             slope2, abase, capl2, csc, ctx, ab_t, dab_t, klo, khi);
+          }
+        } else if (partial) {
+          if constexpr (kDoc) {
+            if (doc_runs)
+              dq_half_math<SK, MK, true, false, true>(sr, pr, pk, nlse2, delta, s_doc, i, di, j0, P.seq_k, P.window, P.stride,
+                                                      c2, slope2, abase, capl2, csc, ctx, nullptr, nullptr, klo, khi);
+            else
+              dq_half_math<SK, MK, true, false, false>(sr, pr, pk, nlse2, delta, s_doc, i, di, j0, P.seq_k, P.window,
+                                                       P.stride, c2, slope2, abase, capl2, csc, ctx);
+          } else {
+            dq_half_math<SK, MK, true>(sr, pr, pk, nlse2, delta, s_doc, i, di, j0, P.seq_k, P.window, P.stride, c2, slope2,
+                                       abase, capl2, csc, ctx, nullptr, nullptr, klo, khi);
+          }
+        } else {
+          dq_half_math<SK, MK, false>(sr, pr, pk, nlse2, delta, s_doc, i, di, j0, P.seq_k, P.window, P.stride, c2, slope2,
+                                      abase, capl2, csc, ctx);
+        }
         if (n > 0) {  // the dQ MMA of the previous tile must have read the dS buffer
           ok = __all_sync(0xffffffffu, ptx::mbar_wait(&sh->bar_dq, (T - 1) & 1));
           if (!ok) { fail_at = 11; continue; }

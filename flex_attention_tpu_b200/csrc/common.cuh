@@ -47,7 +47,7 @@ constexpr int32_t kMapMagic = 0x464c5841;  // "FLXA"
 
 struct MapLayout {
   int n_qt, n_kt, rows, n_t;
-  size_t off_row, off_col, off_doc, off_order, off_order_rm, bytes;
+  size_t off_row, off_col, off_doc, off_order, off_order_rm, off_run_lo, off_run_hi, off_sorted, bytes;
 };
 
 __host__ __device__ inline MapLayout map_layout(int batch, int seq_q, int seq_k, int mask_kind) {
@@ -65,7 +65,15 @@ __host__ __device__ inline MapLayout map_layout(int batch, int seq_q, int seq_k,
   L.off_order = (L.off_doc + doc + 15) & ~(size_t)15;
   // ... and the row-map entries in that order (so that walking the order needs no dependent load)
   L.off_order_rm = (L.off_order + sizeof(int32_t) * (size_t)L.rows * L.n_qt + 15) & ~(size_t)15;
-  L.bytes = (L.off_order_rm + sizeof(int4) * (size_t)L.rows * L.n_qt + 255) & ~(size_t)255;
+  // document masks: first / one-past-last position of the run of equal ids every position sits in, and one flag per
+  // batch row saying that its ids never decrease (then equal ids are contiguous and a row's kept keys are one
+  // interval, so the kernels mask partial tiles from these two numbers instead of comparing ids per element)
+  const size_t len = (size_t)(seq_q > seq_k ? seq_q : seq_k);
+  const size_t runs = (mask_kind == FLEXATTN_MASK_DOCUMENT) ? sizeof(int32_t) * (size_t)batch * len : 0;
+  L.off_run_lo = (L.off_order_rm + sizeof(int4) * (size_t)L.rows * L.n_qt + 15) & ~(size_t)15;
+  L.off_run_hi = (L.off_run_lo + runs + 15) & ~(size_t)15;
+  L.off_sorted = (L.off_run_hi + runs + 15) & ~(size_t)15;
+  L.bytes = (L.off_sorted + (runs ? sizeof(int32_t) * (size_t)batch : 0) + 255) & ~(size_t)255;
   return L;
 }
 
@@ -90,6 +98,9 @@ struct DevParams {
   const int4* col_map;  // [rows][n_kt]
   const int32_t* order;  // [rows][n_qt]: q tiles by decreasing number of kv tiles
   const int4* order_rm;  // [rows][n_qt]: row_map entry of order[i]
+  const int32_t* run_lo;      // document masks: [batch][doc_stride] first position of each position's run of equal ids
+  const int32_t* run_hi;      // ... one past its last position
+  const int32_t* doc_sorted;  // ... [batch] 1 when the row's ids never decrease (runs are whole documents)
   int32_t* status;
   int batch, heads, seq_q, seq_k, head_dim;
   int n_qt, n_kt, map_rows, doc_stride;
@@ -120,8 +131,9 @@ __device__ __forceinline__ bool mask_keep(int i, int j, int window, int stride, 
 }
 
 // For the mask kinds whose kept keys of a query row (and kept queries of a key row) form ONE interval, a partial tile
-// evaluates the mask once per row and 32 columns as a bitmap instead of once per element: bit c of the result says
-// whether column `base + c` is kept (the sequence end included).  Document and S2 masks are not intervals.
+// evaluates the mask once per row and 32 columns as a bitmap (range_bits32 of the row's interval, shifted to the
+// group's first column) instead of once per element.  S2 masks are not intervals; document masks are when the ids of
+// the batch row never decrease.
 template <int MK>
 constexpr bool kMaskIsInterval = MK == FLEXATTN_MASK_NONE || MK == FLEXATTN_MASK_CAUSAL ||
                                  MK == FLEXATTN_MASK_SLIDING_WINDOW || MK == FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL;
@@ -131,24 +143,24 @@ __device__ __forceinline__ uint32_t range_bits32(int lo, int hi) {  // bits [lo,
   if (hi <= lo) return 0u;
   return (hi == 32 ? 0xffffffffu : ((1u << hi) - 1u)) & ~((1u << lo) - 1u);
 }
-// query row i, keys jb .. jb + 31
+// Kept keys [klo, khi) of query row i (the sequence end included) for the interval kinds.
 template <int MK>
-__device__ __forceinline__ uint32_t keep_bits_keys(int i, int jb, int seq_k, int window) {
+__device__ __forceinline__ void row_key_interval(int i, int seq_k, int window, int& klo, int& khi) {
   const bool lower = MK == FLEXATTN_MASK_SLIDING_WINDOW || MK == FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL;  // j > i - window
   const bool upper = MK == FLEXATTN_MASK_CAUSAL || MK == FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL;           // j <= i
-  const int lo = lower ? i - window + 1 : 0;
-  const int hi = upper ? (i + 1 < seq_k ? i + 1 : seq_k) : seq_k;
-  return range_bits32(lo - jb, hi - jb);
+  klo = lower ? i - window + 1 : 0;
+  khi = upper ? (i + 1 < seq_k ? i + 1 : seq_k) : seq_k;
 }
-// key row j, queries ib .. ib + 31
+// Kept queries [qlo, qhi) of key row j.
 template <int MK>
-__device__ __forceinline__ uint32_t keep_bits_queries(int j, int ib, int seq_q, int window) {
+__device__ __forceinline__ void row_query_interval(int j, int seq_q, int window, int& qlo, int& qhi) {
   const bool lower = MK == FLEXATTN_MASK_CAUSAL || MK == FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL;           // i >= j
   const bool upper = MK == FLEXATTN_MASK_SLIDING_WINDOW || MK == FLEXATTN_MASK_SLIDING_WINDOW_CAUSAL;  // i < j + window
-  const int lo = lower ? j : 0;
-  const int hi = upper ? (j + window < seq_q ? j + window : seq_q) : seq_q;
-  return range_bits32(lo - ib, hi - ib);
+  qlo = lower ? j : 0;
+  qhi = upper ? (j + window < seq_q ? j + window : seq_q) : seq_q;
 }
+// A document mask over ids that never decrease is an interval as well: query row i keeps the keys [run_lo(i), i],
+// key row j the queries [j, run_hi(j)), with run_lo / run_hi from the mask map.
 
 // Compile-time score functors on the scaled score s = sm_scale * <q,k>, natural units.
 // score_fwd returns t = score_mod(s) + bias(i, j); score_dsig returns d score_mod / d s.

@@ -44,18 +44,24 @@ struct ScoreCtx {
 };
 
 // x: this thread's 128 raw scores of one tile -> log2-domain logits in place; returns their maximum.
-template <int SK, int MK, bool kPartial>
+// kInterval: the row's kept keys are the interval [klo, khi) (interval mask kinds; documents over sorted ids): a
+// partial tile then tests one bit per element of a bitmap built once per 32 columns.
+template <int SK, int MK, bool kPartial, bool kInterval = kMaskIsInterval<MK>>
 __device__ __forceinline__ float score_row(float (&x)[kTile], int i, int j0, int seq_k, int window, int stride,
                                            float c2, float slope2, float capl2, float csc, int di,
-                                           const int32_t* s_doc, const ScoreCtx ctx) {
+                                           const int32_t* s_doc, const ScoreCtx ctx, int klo = 0, int khi = 0) {
   float mx[4] = {kMasked, kMasked, kMasked, kMasked};
+  uint32_t keep = 0u;  // kept columns of the current group of 32 (kInterval on partial tiles)
   if constexpr (SK == FLEXATTN_SCORE_SOFTCAP || SK == FLEXATTN_SCORE_USER) {
 #pragma unroll
     for (int c = 0; c < kTile; ++c) {
       float t;
       if constexpr (SK == FLEXATTN_SCORE_USER) t = user_score(x[c] * ctx.sm_scale, ctx.b, ctx.h, i, j0 + c) * kLog2e;
       else t = capl2 * ptx::tanh_approx(x[c] * csc);
-      if constexpr (kPartial) {
+      if constexpr (kPartial && kInterval) {
+        if ((c & 31) == 0) keep = range_bits32(klo - (j0 + c), khi - (j0 + c));
+        t = (keep >> (c & 31)) & 1u ? t : kMasked;
+      } else if constexpr (kPartial) {
         const int j = j0 + c;
         const int dj = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c] : 0;
         t = ((j < seq_k) && mask_keep<MK>(i, j, window, stride, di, dj)) ? t : kMasked;
@@ -67,7 +73,6 @@ __device__ __forceinline__ float score_row(float (&x)[kTile], int i, int j0, int
     const float abase = slope2 * (float)(j0 - i);
     uint64_t b2 = ptx::pack2(abase, abase + slope2);
     const uint64_t bstep2 = ptx::pack2(2.f * slope2, 2.f * slope2);
-    uint32_t keep = 0u;  // kept columns of the current group of 32 (interval masks on partial tiles)
 #pragma unroll
     for (int c = 0; c < kTile; c += 2) {
       const uint64_t x2 = ptx::pack2(x[c], x[c + 1]);
@@ -78,8 +83,8 @@ __device__ __forceinline__ float score_row(float (&x)[kTile], int i, int j0, int
       } else {
         ptx::unpack2(ptx::mul2(x2, ptx::pack2(c2, c2)), t0, t1);
       }
-      if constexpr (kPartial && kMaskIsInterval<MK>) {  // one bitmap per row and 32 columns instead of per-element tests
-        if ((c & 31) == 0) keep = keep_bits_keys<MK>(i, j0 + c, seq_k, window);
+      if constexpr (kPartial && kInterval) {  // one bitmap per row and 32 columns instead of per-element tests
+        if ((c & 31) == 0) keep = range_bits32(klo - (j0 + c), khi - (j0 + c));
         t0 = (keep >> (c & 31)) & 1u ? t0 : kMasked;
         t1 = (keep >> ((c & 31) + 1)) & 1u ? t1 : kMasked;
       } else if constexpr (kPartial) {
@@ -299,6 +304,19 @@ __global__ void __launch_bounds__(kThreads, 1)
                     FLEXATTN_DBG_OK((long long)b * P.doc_stride + i, n_doc, 5, 502)) ? doc[i] : 0;
     float m_ref = kMasked, m_true = kMasked, l = 0.f;
     const ScoreCtx ctx{P.sm_scale, b, h};
+    // the interval [klo, khi) of keys this row keeps, where the mask has one: the interval kinds, and a document mask
+    // when the ids of the batch row never decrease (then the mask map holds the start of every row's document)
+    constexpr bool kDoc = MK == FLEXATTN_MASK_DOCUMENT;
+    bool doc_runs = false;
+    int klo = 0, khi = P.seq_k;
+    if constexpr (kMaskIsInterval<MK>) row_key_interval<MK>(i, P.seq_k, P.window, klo, khi);
+    if constexpr (kDoc) {
+      doc_runs = FLEXATTN_DBG_OK(b, P.batch, 5, 506) && P.doc_sorted[b] != 0;
+      if (doc_runs && qt < P.n_qt && i < P.seq_q && FLEXATTN_DBG_OK((long long)b * P.doc_stride + i, n_doc, 5, 507)) {
+        klo = P.run_lo[(size_t)b * P.doc_stride + i];
+        khi = i + 1 < P.seq_k ? i + 1 : P.seq_k;
+      }
+    }
     bool ok = true;
     int fail_at = 0;
 
@@ -306,7 +324,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t par = n & 1;
       const int kt = kv_tile_at<SK>(rms.x, rms.y, n), j0 = kt * kTile;
       const bool partial = !(kt >= rms.z && kt < rms.w);
-      if (MK == FLEXATTN_MASK_DOCUMENT && partial) {
+      if (MK == FLEXATTN_MASK_DOCUMENT && partial && !doc_runs) {
         // one buffer per stream: readers of the previous partial tile are done (first barrier) before the ids of
         // this tile are written; the second barrier publishes them
         ptx::named_bar_sync(1 + s, 128);
@@ -338,7 +356,17 @@ __global__ void __launch_bounds__(kThreads, 1)
       // scores and folds sm_scale*log2e into the FMA that also subtracts the running max)
       float tmax, xs = 1.0f;
       if (partial) {
-        tmax = score_row<SK, MK, true>(x, i, j0, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di, sh->doc[s], ctx);
+        if constexpr (kDoc) {
+          if (doc_runs)
+            tmax = score_row<SK, MK, true, true>(x, i, j0, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di, sh->doc[s],
+                                                 ctx, klo, khi);
+          else
+            tmax = score_row<SK, MK, true, false>(x, i, j0, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di,
+                                                  sh->doc[s], ctx);
+        } else {
+          tmax = score_row<SK, MK, true>(x, i, j0, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di, sh->doc[s], ctx,
+                                         klo, khi);
+        }
       } else if constexpr (SK != FLEXATTN_SCORE_NONE) {
         tmax = score_row<SK, MK, false>(x, i, j0, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di, sh->doc[s], ctx);
       } else {

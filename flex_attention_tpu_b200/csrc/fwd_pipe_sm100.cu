@@ -63,12 +63,15 @@ struct ScoreCtx {
   int b, h;
 };
 
-template <int SK, int MK, bool kPartial, bool kBias = false>
+// kInterval: the row's kept keys are the interval [klo, khi) (interval mask kinds; documents over sorted ids): a
+// partial tile then tests one bit per element of a bitmap built once per 32 columns.
+template <int SK, int MK, bool kPartial, bool kBias = false, bool kInterval = kMaskIsInterval<MK>>
 __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, int c_base, int seq_k, int window,
                                             int stride, float c2, float slope2, float capl2, float csc, int di,
                                             const int32_t* s_doc, const ScoreCtx ctx,
-                                            const float* __restrict__ ab_row = nullptr) {
+                                            const float* __restrict__ ab_row = nullptr, int klo = 0, int khi = 0) {
   float mx[4] = {kMasked, kMasked, kMasked, kMasked};
+  uint32_t keep = 0u;  // kept columns of the current group of 32 (kInterval on partial tiles)
   const float abase = slope2 * (float)(j0 + c_base - i);
   float bias[8];
   if constexpr (SK == FLEXATTN_SCORE_SOFTCAP || SK == FLEXATTN_SCORE_USER) {
@@ -87,7 +90,10 @@ __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, in
         }
         t = fmaf(bias[c & 7], kLog2e, t);
       }
-      if constexpr (kPartial) {
+      if constexpr (kPartial && kInterval) {
+        if ((c & 31) == 0) keep = range_bits32(klo - (j0 + c_base + c), khi - (j0 + c_base + c));
+        t = (keep >> (c & 31)) & 1u ? t : kMasked;
+      } else if constexpr (kPartial) {
         const int j = j0 + c_base + c;
         const int dj = (MK == FLEXATTN_MASK_DOCUMENT) ? s_doc[c_base + c] : 0;
         t = ((j < seq_k) && mask_keep<MK>(i, j, window, stride, di, dj)) ? t : kMasked;
@@ -102,7 +108,6 @@ __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, in
   // rebuilding it from the column numbers
   uint64_t b2 = ptx::pack2(abase, abase + slope2);
   const uint64_t bstep2 = ptx::pack2(2.f * slope2, 2.f * slope2);
-  uint32_t keep = 0u;  // kept columns of the current group of 32 (interval masks on partial tiles)
 #pragma unroll
   for (int c = 0; c < kHalf; c += 2) {
     const uint64_t x2 = ptx::pack2(x[c], x[c + 1]);
@@ -123,8 +128,8 @@ __device__ __forceinline__ float score_half(float (&x)[kHalf], int i, int j0, in
       t0 = fmaf(bias[c & 7], kLog2e, t0);
       t1 = fmaf(bias[(c & 7) + 1], kLog2e, t1);
     }
-    if constexpr (kPartial && kMaskIsInterval<MK>) {
-      if ((c & 31) == 0) keep = keep_bits_keys<MK>(i, j0 + c_base + c, seq_k, window);
+    if constexpr (kPartial && kInterval) {
+      if ((c & 31) == 0) keep = range_bits32(klo - (j0 + c_base + c), khi - (j0 + c_base + c));
       t0 = (keep >> (c & 31)) & 1u ? t0 : kMasked;
       t1 = (keep >> ((c & 31) + 1)) & 1u ? t1 : kMasked;
     } else if constexpr (kPartial) {
@@ -364,6 +369,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int32_t* doc = (MK == FLEXATTN_MASK_DOCUMENT) ? P.doc_ids + (size_t)b * P.doc_stride : nullptr;
       const int di = (MK == FLEXATTN_MASK_DOCUMENT && i < P.seq_q && FLEXATTN_DBG_OK((long long)b * P.doc_stride + i, n_doc, 4, 102))
                          ? doc[i] : 0;
+      // the interval [klo, khi) of keys this row keeps, where the mask has one: the interval kinds, and a document
+      // mask when the ids of the batch row never decrease (then the mask map holds the start of every row's document)
+      constexpr bool kDoc = MK == FLEXATTN_MASK_DOCUMENT;  // (for other kinds the run form below is the default form)
+      bool doc_runs = false;
+      int klo = 0, khi = P.seq_k;
+      if constexpr (kMaskIsInterval<MK>) row_key_interval<MK>(i, P.seq_k, P.window, klo, khi);
+      if constexpr (MK == FLEXATTN_MASK_DOCUMENT) {
+        doc_runs = FLEXATTN_DBG_OK(b, P.batch, 4, 107) && P.doc_sorted[b] != 0;
+        if (doc_runs && i < P.seq_q && FLEXATTN_DBG_OK((long long)b * P.doc_stride + i, n_doc, 4, 108)) {
+          klo = P.run_lo[(size_t)b * P.doc_stride + i];
+          khi = i + 1 < P.seq_k ? i + 1 : P.seq_k;
+        }
+      }
       float m_ref = kMasked, m_true = kMasked, l = 0.f;  // l: sum over this thread's columns only
       // dense bias of this query row (nullptr: no bias, or a row past the end of the sequence)
       const float* ab_q = (P.ab != nullptr && i < P.seq_q && FLEXATTN_DBG_OK((long long)bh * P.seq_q + i, n_rows, 4, 103))
@@ -375,7 +393,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t colS = (uint32_t)sb * 128u;
         const int kt = kv_tile_at<SK>(rm.x, rm.y, n), j0 = kt * kTile;
         const bool partial = P.ab != nullptr || !(kt >= rm.z && kt < rm.w);
-        if (MK == FLEXATTN_MASK_DOCUMENT && partial && half == 0) {
+        if (MK == FLEXATTN_MASK_DOCUMENT && partial && !doc_runs && half == 0) {
           const int j = j0 + row;
           sh->doc[par][row] = (j < P.seq_k && FLEXATTN_DBG_OK((long long)b * P.doc_stride + j, n_doc, 4, 104)) ? doc[j] : -1;
         }
@@ -399,7 +417,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int c = 0; c < 32; ++c) x[q2 * 32 + c] = __uint_as_float(xr[q2][c]);
           }
         }
-        if (MK == FLEXATTN_MASK_DOCUMENT && partial) ptx::named_bar_sync(2, 256);  // kv-tile document ids visible
+        if (MK == FLEXATTN_MASK_DOCUMENT && partial && !doc_runs) ptx::named_bar_sync(2, 256);  // kv-tile document ids visible
         // xs: factor still to be applied to x inside the exp2 argument (the plain-score fast path keeps the raw
         // scores and folds sm_scale*log2e into the FMA that also subtracts the running max)
         float tmax = kMasked, xs = 1.0f;
@@ -407,11 +425,30 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (P.ab != nullptr) {
             // with a bias every tile takes the masked form (the mask functor also clips the ragged last tile):
             // the S^2 floats of the bias bound this path, not the arithmetic
-            tmax = score_half<SK, MK, true, true>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc,
-                                                  di, sh->doc[par], ctx, ab_q != nullptr ? ab_q + j0 + c_base : nullptr);
+            const float* ab_t = ab_q != nullptr ? ab_q + j0 + c_base : nullptr;
+            if constexpr (kDoc) {
+              if (doc_runs)
+                tmax = score_half<SK, MK, true, true, true>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2,
+                                                            capl2, csc, di, sh->doc[par], ctx, ab_t, klo, khi);
+              else
+                tmax = score_half<SK, MK, true, true, false>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2,
+                                                             capl2, csc, di, sh->doc[par], ctx, ab_t);
+            } else {
+              tmax = score_half<SK, MK, true, true>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc,
+                                                    di, sh->doc[par], ctx, ab_t, klo, khi);
+            }
           } else if (partial) {
-            tmax = score_half<SK, MK, true>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di,
-                                            sh->doc[par], ctx);
+            if constexpr (kDoc) {
+              if (doc_runs)
+                tmax = score_half<SK, MK, true, false, true>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2,
+                                                             capl2, csc, di, sh->doc[par], ctx, nullptr, klo, khi);
+              else
+                tmax = score_half<SK, MK, true, false, false>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2,
+                                                              capl2, csc, di, sh->doc[par], ctx);
+            } else {
+              tmax = score_half<SK, MK, true>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di,
+                                              sh->doc[par], ctx, nullptr, klo, khi);
+            }
           } else if constexpr (SK != FLEXATTN_SCORE_NONE) {
             tmax = score_half<SK, MK, false>(x, i, j0, c_base, P.seq_k, P.window, P.stride, c2, slope2, capl2, csc, di,
                                              sh->doc[par], ctx);

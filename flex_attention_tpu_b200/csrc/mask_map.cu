@@ -71,6 +71,86 @@ __global__ void doc_minmax_kernel(const int32_t* __restrict__ doc_ids, int2* __r
   }
 }
 
+// Runs of equal document ids, one CTA of 1024 threads per batch row: run_lo[p] / run_hi[p] = first / one past the
+// last position of the run position p sits in (an inclusive prefix-maximum scan of the run starts and a suffix-minimum
+// scan of the run ends, in chunks of 1024 with a carry), and sorted[b] = 1 when the ids never decrease.
+__global__ void __launch_bounds__(1024) doc_runs_kernel(const int32_t* __restrict__ doc_ids, int32_t* __restrict__ run_lo,
+                                                        int32_t* __restrict__ run_hi, int32_t* __restrict__ sorted, int len) {
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int32_t* doc = doc_ids + (size_t)b * len;
+  int32_t* lo = run_lo + (size_t)b * len;
+  int32_t* hi = run_hi + (size_t)b * len;
+  __shared__ int warp_v[32];
+  __shared__ int carry_s, unsorted_s;
+  if (tid == 0) { carry_s = 0; unsorted_s = 0; }
+  __syncthreads();
+  for (int base = 0; base < len; base += 1024) {  // forward: latest run start at or before p
+    const int p = base + tid;
+    int v = -1;
+    if (p < len) {
+      const int d = doc[p];
+      if (p == 0) v = 0;
+      else {
+        const int dp = doc[p - 1];
+        if (d != dp) v = p;
+        if (d < dp) unsorted_s = 1;
+      }
+    }
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, v, s);
+      if (lane >= s) v = max(v, o);
+    }
+    if (lane == 31) warp_v[w] = v;
+    __syncthreads();
+    if (w == 0) {
+      int x = warp_v[lane];
+#pragma unroll
+      for (int s = 1; s < 32; s <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, x, s);
+        if (lane >= s) x = max(x, o);
+      }
+      warp_v[lane] = x;
+    }
+    __syncthreads();
+    v = max(v, max(carry_s, w > 0 ? warp_v[w - 1] : -1));
+    if (p < len) lo[p] = v;
+    __syncthreads();
+    if (tid == 1023) carry_s = v;
+    __syncthreads();
+  }
+  if (tid == 0) carry_s = len;
+  __syncthreads();
+  for (int base = ((len - 1) / 1024) * 1024; base >= 0; base -= 1024) {  // backward: earliest run end after p
+    const int p = base + 1023 - tid;  // thread order = descending position
+    int v = 0x7fffffff;
+    if (p < len && (p == len - 1 || doc[p + 1] != doc[p])) v = p + 1;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, v, s);
+      if (lane >= s) v = min(v, o);
+    }
+    if (lane == 31) warp_v[w] = v;
+    __syncthreads();
+    if (w == 0) {
+      int x = warp_v[lane];
+#pragma unroll
+      for (int s = 1; s < 32; s <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, x, s);
+        if (lane >= s) x = min(x, o);
+      }
+      warp_v[lane] = x;
+    }
+    __syncthreads();
+    v = min(v, min(carry_s, w > 0 ? warp_v[w - 1] : 0x7fffffff));
+    if (p < len) hi[p] = v;
+    __syncthreads();
+    if (tid == 1023) carry_s = v;
+    __syncthreads();
+  }
+  if (tid == 0) sorted[b] = unsorted_s ? 0 : 1;
+}
+
 __global__ void mask_map_kernel(MapHeader hdr, MapHeader* __restrict__ hdr_out, int4* __restrict__ row_map,
                                 int4* __restrict__ col_map, const int2* __restrict__ docmm, int n_t) {
   if (blockIdx.x == 0 && threadIdx.x == 0) *hdr_out = hdr;
@@ -160,6 +240,9 @@ cudaError_t launch_mask_map(cudaStream_t st, const FlexAttnParams& p) {
     docmm = reinterpret_cast<int2*>(ws + L.off_doc);
     const int len = p.seq_q > p.seq_k ? p.seq_q : p.seq_k;
     doc_minmax_kernel<<<dim3(L.n_t, p.batch), 128, 0, st>>>(p.doc_ids, docmm, L.n_t, len);
+    doc_runs_kernel<<<p.batch, 1024, 0, st>>>(p.doc_ids, reinterpret_cast<int32_t*>(ws + L.off_run_lo),
+                                              reinterpret_cast<int32_t*>(ws + L.off_run_hi),
+                                              reinterpret_cast<int32_t*>(ws + L.off_sorted), len);
   }
   const int entries = L.rows * (L.n_qt + L.n_kt);
   const int blocks = (entries + 127) / 128;

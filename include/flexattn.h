@@ -101,7 +101,9 @@ typedef struct FlexAttnParams {
   float* l;          /* [B,H,Sq]  sum_j exp(x - m)   (fwd output, bwd input) */
   float* m;          /* [B,H,Sq]  row max of x       (fwd output, bwd input) */
   float* delta;      /* [B,H,Sq]  rowsum(o * do)     (bwd_preprocess output, dq/dkv input) */
-  const int32_t* doc_ids;     /* [B, max(Sq,Sk)] document id per position; MASK_DOCUMENT only */
+  const int32_t* doc_ids;     /* [B, max(Sq,Sk)] document id per position; MASK_DOCUMENT only.  A pair is kept when
+                               * the ids are EQUAL (and the key is not ahead of the query); any ids are valid, ids
+                               * that never decrease along a batch row (documents laid end to end) run fastest */
   const float* alibi_slopes;  /* [H]; SCORE_ALIBI only */
   /* problem */
   int32_t batch, heads, seq_q, seq_k, head_dim;

@@ -196,3 +196,31 @@ def test_error_is_operand_and_store_rounding():
     corr = float(np.dot(eg, em) / (np.linalg.norm(eg) * np.linalg.norm(em)))
     print("parity", {"case": "error model dv", "error_correlation": corr})
     assert corr >= 0.7, corr
+
+
+@pytest.mark.parametrize("ids", ["repeating", "descending", "one_row_unsorted"])
+@pytest.mark.parametrize("score_kind,D", [("none", 128), ("softcap", 64)])
+def test_document_ids_need_not_be_sorted(ids, score_kind, D):
+    """The document mask is defined by EQUAL ids.  When the ids of a batch row never decrease the kernels mask
+    partial tiles from the bounds of each position's run of equal ids (computed once with the mask map); otherwise
+    an id may come back after another one, a row's kept keys are no interval, and the kernels compare ids per
+    element.  Both forms, and a batch that mixes them, against the oracle."""
+    fa = _fa()
+    B, H, S = 2, 2, 700
+    pos = np.arange(S)
+    if ids == "repeating":
+        doc = np.stack([(pos // 90) % 3, (pos // 130) % 2]).astype(np.int32)            # ids come back
+    elif ids == "descending":
+        doc = np.stack([7 - pos // 100, 9 - pos // 64]).astype(np.int32)                # contiguous runs, decreasing ids
+    else:
+        doc = np.stack([pos // 150, (pos // 90) % 3]).astype(np.int32)                  # row 0 sorted, row 1 not
+    (q, k, v, do), host = make_qkvdo((B, H, S, D), (B, H, S, D), 321, torch.bfloat16)
+    cap = 4.0 if score_kind == "softcap" else None
+    sm_scale = 1.0 / np.sqrt(D)
+    for fwd_backend in ("tcgen05",):
+        status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        got = run_hot_path(fa, q, k, v, do, sm_scale=sm_scale, mask_kind="document", score_kind=score_kind,
+                           backend=fwd_backend, doc_ids=doc, cap=cap or 0.0, status=status)
+        assert status.tolist() == [0, 0, 0, 0], status.tolist()
+        want = oracle_hot_path(*host, sm_scale=sm_scale, mask_kind="document", score_kind=score_kind, doc_ids=doc, cap=cap)
+        assert_close(got, want, torch.bfloat16, what=f"document ids {ids}/{score_kind}/D{D}")
