@@ -406,7 +406,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (row < 64) {
         // pre-scaled for pack_bf16_trunc; l == 0 (fully masked row) forces p to 0
         sh->nlse2[st][64 * half + row] =
-            pf_ok ? (pf_l > 0.f ? ptx::kRoundLog2 - fmaf(pf_m, kLog2e, log2f(pf_l)) : -1.0e30f) : ptx::kRoundLog2;
+            pf_ok ? (pf_l > 0.f ? ptx::kRoundLog2 - fmaf(pf_m, kLog2e, __log2f(pf_l)) : -1.0e30f) : ptx::kRoundLog2;
       } else {
         const int r = row - 64;
         const int i = (cm.x + n) * kTile + 64 * half + r;
